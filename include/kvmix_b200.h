@@ -1,0 +1,182 @@
+/*
+ * kvmix_b200 -- C ABI of the B200 (sm_100a) KV-cache hot path: group quantizer, dequant GEMV
+ * and fused decode attention over a mixed-precision (1/2/3/4-bit + fp16 tail) KV cache.
+ *
+ * Every entry point takes plain device pointers, sizes and element strides, launches on the
+ * stream it is given, never synchronises the host, never allocates, and returns 0 or a negative
+ * KVQ_ERR_* code detected on the host before any launch.  Launch errors are returned as
+ * KVQ_ERR_CUDA (kvq_last_cuda_error() gives the CUDA text).
+ *
+ * Formats (identical to the upstream KVmix extension, so buffers are interchangeable):
+ *   codes   int32 words, fields LSB first; 32/b fields of b bits for b in {1,2,4}; b = 3 packs 11
+ *           fields per word: ten 3-bit fields at bits 0..29 and one 2-bit field at bits 30..31
+ *           (upstream quant_cuda/csrc/quantization_cuda.cu:612-626)
+ *   scale   (max-min)/(2^b-1) of each group, computed in fp32, stored in the input dtype
+ *   mn      min of each group ("zero")
+ *   dequantised value = scale * code + mn
+ */
+#ifndef KVMIX_B200_H
+#define KVMIX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st *kvq_stream_t; /* a cudaStream_t */
+
+enum {
+    KVQ_OK = 0,
+    KVQ_ERR_BITS = -1,        /* bits not in {1,2,3,4}                               */
+    KVQ_ERR_GROUP3 = -2,      /* 3-bit requires group 11                             */
+    KVQ_ERR_DIV11 = -3,       /* 3-bit requires length divisible by 11               */
+    KVQ_ERR_DIVGROUP = -4,    /* length not divisible by group                       */
+    KVQ_ERR_DIVWORD = -5,     /* length not divisible by 32/bits                     */
+    KVQ_ERR_HEADS = -6,       /* query heads not divisible by kv heads               */
+    KVQ_ERR_SHAPE = -7,       /* inconsistent sizes                                  */
+    KVQ_ERR_GROUPWORD = -8,   /* group not a multiple of 32/bits where one is needed */
+    KVQ_ERR_TOKENS = -9,      /* K and V token counts differ                         */
+    KVQ_ERR_NULL = -10,       /* null pointer                                        */
+    KVQ_ERR_UNSUPPORTED = -11,/* outside what the kernels implement (see each call)  */
+    KVQ_ERR_WORKSPACE = -12,  /* workspace missing or too small                      */
+    KVQ_ERR_ALIGN = -13,      /* pointer or stride alignment                         */
+    KVQ_ERR_CUDA = -100       /* a CUDA call or launch failed                        */
+};
+
+int kvq_version(void);
+const char *kvq_error_string(int code);
+const char *kvq_last_cuda_error(void);
+
+/* Fields per 32-bit word: 32/bits, or 11 for bits == 3. */
+int kvq_features_per_int(int bits);
+
+/*
+ * Group quantizer along the last dimension of a 4-D tensor.
+ * Replaces quantize_pack_last_dim_cuda, upstream quant_cuda/csrc/quantization_cuda.cu:631-721
+ * (kernels :540-598 and :601-629), and -- through the output strides -- the append forms
+ * process_key_quantization_cuda (:298-411) and process_value_quantization_cuda (:413-537):
+ * point code/scale/mn at the first free word/group of a preallocated cache and the new
+ * groups are written in place.
+ *
+ * x is logically [B, H, A, S]; element (b,h,a,s) is at x[b*x_sB + h*x_sH + a*x_sA + s*x_sS]
+ * (strides in elements), so a [B,H,T,D] key tensor is quantized per channel over token groups
+ * by passing A = D, S = T, x_sA = 1, x_sS = D without a transposed copy.
+ * Groups of `group` consecutive s.  Outputs:
+ *   code  [B,H,A,S/fpi] int32   strides c_sB, c_sH, c_sA (words), last dim contiguous
+ *   scale [B,H,A,S/group]       strides z_sB, z_sH, z_sA (elements), last dim contiguous
+ *   mn    same shape and strides as scale
+ * x_is_f32 = 0: x, scale, mn are fp16;  1: they are fp32.
+ * Rules (same as upstream): bits == 3 needs group == 11 and S % 11 == 0; otherwise
+ * S % group == 0 and S % (32/bits) == 0.
+ */
+typedef struct {
+    const void *x;
+    int32_t x_is_f32;
+    int64_t B, H, A, S;
+    int64_t x_sB, x_sH, x_sA, x_sS;
+    int32_t group, bits;
+    int32_t *code;
+    int64_t c_sB, c_sH, c_sA;
+    void *scale;
+    void *mn;
+    int64_t z_sB, z_sH, z_sA;
+} kvq_quant_args;
+
+int kvq_quant_lastdim(const kvq_quant_args *a, kvq_stream_t stream);
+
+/*
+ * Dequantising mat-vec, M = 1.
+ * Replaces quantized_gemm, upstream quant_cuda/csrc/dequantization_gemv_cuda.cu:127-248 (kernel
+ * :7-124), reading the caller's layout directly (upstream first transposes codes, scales and
+ * zeros on every call, :151-171):
+ *   out[b,h,n] = fp16( sum_k fA[b,h,k] * (scale[b,hk,k,n/group] * code[b,hk,k,n] + zero[b,hk,k,n/group]) )
+ *   hk = h / (nh / nh_kv), fp32 accumulation.
+ *   fA    [B, nh, K] fp16                 strides a_sB, a_sH, K contiguous
+ *   qB    [B, nh_kv, K, n_words] int32    strides q_sB, q_sH, q_sK (words)
+ *   scale [B, nh_kv, K, n_groups] fp16    strides s_sB, s_sH, s_sK; zeros alike
+ *   out   [B, nh, N] fp16, N = n_groups * group, strides o_sB, o_sH
+ * group must be a multiple of 32/bits (11 for bits == 3): one scale per packed word, as upstream.
+ */
+typedef struct {
+    const void *fA;
+    int64_t a_sB, a_sH;
+    const int32_t *qB;
+    int64_t q_sB, q_sH, q_sK;
+    const void *scale;
+    const void *zero;
+    int64_t s_sB, s_sH, s_sK;
+    void *out;
+    int64_t o_sB, o_sH;
+    int64_t B, nh, nh_kv, K, n_words, n_groups;
+    int32_t group, bits;
+} kvq_gemv_args;
+
+int kvq_gemv(const kvq_gemv_args *a, kvq_stream_t stream);
+
+/*
+ * Fused decode attention for one query token per sequence over a mixed cache:
+ *   scores = [ q.Kq^T (packed keys, tokens 0..Tkq) | q.Kfull^T (fp16 keys, tokens Tkq..T) ] / sqrt(D)
+ *   p = softmax(scores);  out = p[:Tvq].Vq (packed values) + p[Tvq:].Vfull (fp16 values)
+ * Replaces, in one launch, the cached branch of the upstream attention forward
+ * (models/modeling_llama_KVmix.py:170-211, models/modeling_mistral_KVmix.py:207-262): two
+ * quantized_gemm calls, repeat_kv_quant copies, two fp16 matmuls, concat, softmax and add.
+ * The key and value boundaries Tkq and Tvq are independent (upstream uses different group sizes
+ * and residual ratios for K and V).  GQA is native: query head h reads kv head h/(nh/nh_kv).
+ *
+ *   q      [B, nh, D] fp16              strides q_sB, q_sH
+ *   out    [B, nh, D] fp16              strides o_sB, o_sH
+ *   kcode  [B, nh_kv, D, Tkq/fpi_k]     strides kc_sB, kc_sH, kc_sD (words)
+ *   kscale, kmn [B, nh_kv, D, Tkq/k_group] fp16, strides ks_sB, ks_sH, ks_sD
+ *   kfull  [B, nh_kv, kf_cap, D] fp16   strides kf_sB, kf_sH, kf_sT; token Tkq+r lives in row
+ *          (kf_start + r) mod kf_cap  (kf_start = 0 and kf_cap >= Rk for a linear tail)
+ *   vcode  [B, nh_kv, Tvq, D/fpi_v]     strides vc_sB, vc_sH, vc_sT (words)
+ *   vscale, vmn [B, nh_kv, Tvq, D/v_group] fp16, strides vs_sB, vs_sH, vs_sT
+ *   vfull  [B, nh_kv, vf_cap, D] fp16   strides vf_sB, vf_sH, vf_sT, ring like kfull
+ * D must be 128.  k_group and v_group must be multiples of the fields per word (k_group == 11 for
+ * 3-bit keys); 3-bit values need D % 11 == 0 upstream and are rejected here for D = 128.
+ * round_scores != 0 narrows each raw score to fp16 before scaling, as upstream's GEMV and fp16
+ * matmul do; everything else accumulates in fp32.
+ *
+ * workspace: kvq_decode_attn_workspace_bytes(B, nh, T) bytes of device memory (split partials and
+ * one counter per query head).  The call zeroes the counters itself; concurrent calls must not
+ * share a workspace.
+ */
+typedef struct {
+    int32_t B, nh, nh_kv, D;
+    int32_t T, Tkq, Tvq;
+    int32_t k_bits, k_group, v_bits, v_group;
+    int32_t round_scores;
+    float softmax_scale;
+    const void *q;
+    int64_t q_sB, q_sH;
+    void *out;
+    int64_t o_sB, o_sH;
+    const int32_t *kcode;
+    int64_t kc_sB, kc_sH, kc_sD;
+    const void *kscale;
+    const void *kmn;
+    int64_t ks_sB, ks_sH, ks_sD;
+    const void *kfull;
+    int64_t kf_sB, kf_sH, kf_sT;
+    int32_t kf_cap, kf_start;
+    const int32_t *vcode;
+    int64_t vc_sB, vc_sH, vc_sT;
+    const void *vscale;
+    const void *vmn;
+    int64_t vs_sB, vs_sH, vs_sT;
+    const void *vfull;
+    int64_t vf_sB, vf_sH, vf_sT;
+    int32_t vf_cap, vf_start;
+    void *workspace;
+    uint64_t workspace_bytes;
+} kvq_attn_args;
+
+uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32_t T);
+int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVMIX_B200_H */

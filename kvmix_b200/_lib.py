@@ -1,0 +1,92 @@
+"""ctypes binding of libkvmix_b200.so (declared in include/kvmix_b200.h).
+
+There is no fallback: if the library has not been built (``python -m kvmix_b200.build``) importing
+any operator raises.  Struct layouts below mirror the header field for field.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libkvmix_b200.so")
+
+i32, i64, u64, vp = C.c_int32, C.c_int64, C.c_uint64, C.c_void_p
+
+
+class QuantArgs(C.Structure):
+    _fields_ = [("x", vp), ("x_is_f32", i32),
+                ("B", i64), ("H", i64), ("A", i64), ("S", i64),
+                ("x_sB", i64), ("x_sH", i64), ("x_sA", i64), ("x_sS", i64),
+                ("group", i32), ("bits", i32),
+                ("code", vp), ("c_sB", i64), ("c_sH", i64), ("c_sA", i64),
+                ("scale", vp), ("mn", vp), ("z_sB", i64), ("z_sH", i64), ("z_sA", i64)]
+
+
+class GemvArgs(C.Structure):
+    _fields_ = [("fA", vp), ("a_sB", i64), ("a_sH", i64),
+                ("qB", vp), ("q_sB", i64), ("q_sH", i64), ("q_sK", i64),
+                ("scale", vp), ("zero", vp), ("s_sB", i64), ("s_sH", i64), ("s_sK", i64),
+                ("out", vp), ("o_sB", i64), ("o_sH", i64),
+                ("B", i64), ("nh", i64), ("nh_kv", i64), ("K", i64), ("n_words", i64), ("n_groups", i64),
+                ("group", i32), ("bits", i32)]
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [("B", i32), ("nh", i32), ("nh_kv", i32), ("D", i32),
+                ("T", i32), ("Tkq", i32), ("Tvq", i32),
+                ("k_bits", i32), ("k_group", i32), ("v_bits", i32), ("v_group", i32),
+                ("round_scores", i32), ("softmax_scale", C.c_float),
+                ("q", vp), ("q_sB", i64), ("q_sH", i64),
+                ("out", vp), ("o_sB", i64), ("o_sH", i64),
+                ("kcode", vp), ("kc_sB", i64), ("kc_sH", i64), ("kc_sD", i64),
+                ("kscale", vp), ("kmn", vp), ("ks_sB", i64), ("ks_sH", i64), ("ks_sD", i64),
+                ("kfull", vp), ("kf_sB", i64), ("kf_sH", i64), ("kf_sT", i64),
+                ("kf_cap", i32), ("kf_start", i32),
+                ("vcode", vp), ("vc_sB", i64), ("vc_sH", i64), ("vc_sT", i64),
+                ("vscale", vp), ("vmn", vp), ("vs_sB", i64), ("vs_sH", i64), ("vs_sT", i64),
+                ("vfull", vp), ("vf_sB", i64), ("vf_sH", i64), ("vf_sT", i64),
+                ("vf_cap", i32), ("vf_start", i32),
+                ("workspace", vp), ("workspace_bytes", u64)]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded C-ABI library; raises if it is not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m kvmix_b200.build` (needs nvcc). "
+                "kvmix_b200 has no CPU or PyTorch fallback.")
+        L = C.CDLL(LIB_PATH)
+        L.kvq_version.restype = C.c_int
+        L.kvq_error_string.restype = C.c_char_p
+        L.kvq_error_string.argtypes = [C.c_int]
+        L.kvq_last_cuda_error.restype = C.c_char_p
+        L.kvq_features_per_int.restype = C.c_int
+        L.kvq_features_per_int.argtypes = [C.c_int]
+        L.kvq_quant_lastdim.restype = C.c_int
+        L.kvq_quant_lastdim.argtypes = [C.POINTER(QuantArgs), vp]
+        L.kvq_gemv.restype = C.c_int
+        L.kvq_gemv.argtypes = [C.POINTER(GemvArgs), vp]
+        L.kvq_decode_attn.restype = C.c_int
+        L.kvq_decode_attn.argtypes = [C.POINTER(AttnArgs), vp]
+        L.kvq_decode_attn_workspace_bytes.restype = u64
+        L.kvq_decode_attn_workspace_bytes.argtypes = [i32, i32, i32]
+        _lib = L
+    return _lib
+
+
+EXPORTS = ["kvq_version", "kvq_error_string", "kvq_last_cuda_error", "kvq_features_per_int",
+           "kvq_quant_lastdim", "kvq_gemv", "kvq_decode_attn", "kvq_decode_attn_workspace_bytes"]
+
+
+def check(rc):
+    """Negative status -> RuntimeError carrying the upstream TORCH_CHECK wording where one exists."""
+    if rc == 0:
+        return
+    msg = lib().kvq_error_string(rc).decode()
+    if rc == -100:
+        msg += ": " + lib().kvq_last_cuda_error().decode()
+    raise RuntimeError(msg)

@@ -1,0 +1,326 @@
+// Group quantizer: fp16/fp32 -> b-bit codes packed in int32 words + per-group scale and min.
+//
+// Arithmetic (must be bit-identical to upstream quant_cuda/csrc/quantization_cuda.cu:553-596 with
+// IEEE division; this file is compiled without fast-math):
+//   mn, mx   fp32 min / max of the group
+//   scale32  (mx - mn) / (2^b - 1)
+//   code     clamp(roundf((x - mn) / scale32), 0, 2^b - 1), roundf = half away from zero;
+//            3-bit: the 11th element of each group clamps to 3; 0/0 (constant group) -> 0
+//   stored scale = scale32 narrowed to the input dtype, stored mn = mn
+//
+// Three kernels, one result:
+//   quant_contig_kernel   groups run along the contiguous axis (values: [.., T, D], groups over D;
+//                         or keys already transposed to [.., D, T]).  A thread owns one output
+//                         word; the threads of a group combine min/max with shuffles.
+//   quant_strided_kernel  groups run along a strided axis while the *other* axis is contiguous
+//                         (keys left as [.., T, D], groups over T).  A thread owns two adjacent
+//                         channels, keeps a whole group in registers (all loads in flight at
+//                         once), and the CTA transposes words through shared memory so global
+//                         writes are contiguous runs per channel.
+//   quant_generic_kernel  any strides / any group-to-word relation; one thread per word.
+#include "common.cuh"
+
+namespace kvq {
+
+// q = clamp(roundf(n), 0, emax) for n >= 0 or NaN.  n - trunc(n) is exact for these magnitudes,
+// so comparing the fraction with 0.5 is roundf's half-away-from-zero rule.
+__device__ __forceinline__ int round_code(float n, int emax) {
+    int k = (n == n) ? __float2int_rz(n) : 0;
+    float frac = n - (float)k;
+    k += (frac >= 0.5f) ? 1 : 0;
+    return max(0, min(k, emax));
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+
+struct QuantDims {
+    int64_t B, H, A, S;
+    int64_t x_sB, x_sH, x_sA, x_sS;
+    int64_t c_sB, c_sH, c_sA;
+    int64_t z_sB, z_sH, z_sA;
+    int group;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Contiguous groups.  E = fields per word elements per thread, TPG = group / E threads per group.
+template <int BITS, typename T>
+__global__ void __launch_bounds__(256) quant_contig_kernel(const T *__restrict__ x, int32_t *__restrict__ code,
+                                                           T *__restrict__ scale, T *__restrict__ mn, QuantDims d,
+                                                           int tpg, bool vec_ok) {
+    constexpr int E = fields_per_word(BITS);
+    const int64_t words_per_row = d.S / E;
+    const int64_t total = d.B * d.H * d.A * words_per_row;
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool active = idx < total;
+    if (!active) idx = total - 1;  // keep the lane alive for the shuffles
+    const int64_t row = idx / words_per_row, w = idx % words_per_row;
+    const int64_t a = row % d.A, h = (row / d.A) % d.H, b = row / (d.A * d.H);
+    const T *px = x + b * d.x_sB + h * d.x_sH + a * d.x_sA + w * E;
+
+    float v[E];
+    if constexpr (sizeof(T) == 2 && (E % 8 == 0)) {
+        if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < E / 8; ++j) {
+                uint4 u = __ldg(reinterpret_cast<const uint4 *>(px) + j);
+                const __half2 *hp = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float2 f = __half22float2(hp[k]);
+                    v[j * 8 + 2 * k] = f.x;
+                    v[j * 8 + 2 * k + 1] = f.y;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[i] = to_f32<T>(px[i]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[i] = to_f32<T>(px[i]);
+    }
+    float lo = v[0], hi = v[0];
+#pragma unroll
+    for (int i = 1; i < E; ++i) { lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]); }
+    for (int o = 1; o < tpg; o <<= 1) {
+        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    constexpr int QMAX = (1 << BITS) - 1;
+    const float sc = (hi - lo) / (float)QMAX;
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        const float n = (v[i] - lo) / sc;
+        if constexpr (BITS == 3) {
+            const int q = round_code(n, i < 10 ? 7 : 3);
+            word |= (uint32_t)q << (i < 10 ? 3 * i : 30);
+        } else {
+            word |= (uint32_t)round_code(n, QMAX) << (BITS * i);
+        }
+    }
+    if (active) {
+        code[b * d.c_sB + h * d.c_sH + a * d.c_sA + w] = (int32_t)word;
+        if ((w % tpg) == 0) {
+            const int64_t zo = b * d.z_sB + h * d.z_sH + a * d.z_sA + w / tpg;
+            scale[zo] = from_f32<T>(sc);
+            mn[zo] = from_f32<T>(lo);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Strided groups over s, contiguous channel axis a (x_sA == 1), fp16, A % 128 == 0.
+// CTA: 256 threads = 64 channel pairs x 4 group slots; covers 128 channels x GPC groups.
+template <int BITS, int G>
+struct StridedCfg {
+    static constexpr int FPI = fields_per_word(BITS);
+    static constexpr int WPG = G / FPI;                       // words per group (1 for 3-bit)
+    static constexpr int GPC = (G == 11) ? 24 : (256 / G < 4 ? 4 : 256 / G);  // groups per CTA
+    static constexpr int WPC = GPC * WPG;                     // words per channel per CTA
+    static constexpr int WPAD = WPC + 1;
+};
+
+template <int BITS, int G>
+__global__ void __launch_bounds__(256) quant_strided_kernel(const __half *__restrict__ x, int32_t *__restrict__ code,
+                                                            __half *__restrict__ scale, __half *__restrict__ mn,
+                                                            QuantDims d) {
+    using C = StridedCfg<BITS, G>;
+    __shared__ int32_t s_code[128 * C::WPAD];
+    __shared__ __half s_scale[128 * (C::GPC + 2)];
+    __shared__ __half s_mn[128 * (C::GPC + 2)];
+
+    const int pair = threadIdx.x & 63, slot = threadIdx.x >> 6;
+    const int64_t bh = blockIdx.z, b = bh / d.H, h = bh % d.H;
+    const int64_t a0 = (int64_t)blockIdx.y * 128;
+    const int64_t g0 = (int64_t)blockIdx.x * C::GPC;          // first group of this CTA
+    const int64_t n_groups = d.S / G;
+    const int groups_here = (int)min((int64_t)C::GPC, n_groups - g0);
+    const __half *px = x + b * d.x_sB + h * d.x_sH + (a0 + 2 * pair);
+    constexpr int QMAX = (1 << BITS) - 1;
+
+    for (int g = slot; g < groups_here; g += 4) {
+        const __half *pg = px + (g0 + g) * G * d.x_sS;
+        __half2 raw[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) raw[i] = __ldg(reinterpret_cast<const __half2 *>(pg + i * d.x_sS));
+        float lo0, hi0, lo1, hi1;
+        {
+            float2 f = __half22float2(raw[0]);
+            lo0 = hi0 = f.x; lo1 = hi1 = f.y;
+        }
+#pragma unroll
+        for (int i = 1; i < G; ++i) {
+            float2 f = __half22float2(raw[i]);
+            lo0 = fminf(lo0, f.x); hi0 = fmaxf(hi0, f.x);
+            lo1 = fminf(lo1, f.y); hi1 = fmaxf(hi1, f.y);
+        }
+        const float sc0 = (hi0 - lo0) / (float)QMAX, sc1 = (hi1 - lo1) / (float)QMAX;
+#pragma unroll
+        for (int w = 0; w < C::WPG; ++w) {
+            uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+            for (int i = 0; i < C::FPI; ++i) {
+                float2 f = __half22float2(raw[w * C::FPI + i]);
+                const float n0 = (f.x - lo0) / sc0, n1 = (f.y - lo1) / sc1;
+                if constexpr (BITS == 3) {
+                    const int em = i < 10 ? 7 : 3, sh = i < 10 ? 3 * i : 30;
+                    w0 |= (uint32_t)round_code(n0, em) << sh;
+                    w1 |= (uint32_t)round_code(n1, em) << sh;
+                } else {
+                    w0 |= (uint32_t)round_code(n0, QMAX) << (BITS * i);
+                    w1 |= (uint32_t)round_code(n1, QMAX) << (BITS * i);
+                }
+            }
+            s_code[(2 * pair) * C::WPAD + g * C::WPG + w] = (int32_t)w0;
+            s_code[(2 * pair + 1) * C::WPAD + g * C::WPG + w] = (int32_t)w1;
+        }
+        s_scale[(2 * pair) * (C::GPC + 2) + g] = __float2half_rn(sc0);
+        s_scale[(2 * pair + 1) * (C::GPC + 2) + g] = __float2half_rn(sc1);
+        s_mn[(2 * pair) * (C::GPC + 2) + g] = __float2half_rn(lo0);
+        s_mn[(2 * pair + 1) * (C::GPC + 2) + g] = __float2half_rn(lo1);
+    }
+    __syncthreads();
+    const int words_here = groups_here * C::WPG;
+    int32_t *pc = code + b * d.c_sB + h * d.c_sH + a0 * d.c_sA + g0 * C::WPG;
+    for (int i = threadIdx.x; i < 128 * words_here; i += 256) {
+        const int ch = i / words_here, w = i % words_here;
+        pc[ch * d.c_sA + w] = s_code[ch * C::WPAD + w];
+    }
+    const int64_t zo = b * d.z_sB + h * d.z_sH + a0 * d.z_sA + g0;
+    for (int i = threadIdx.x; i < 128 * groups_here; i += 256) {
+        const int ch = i / groups_here, g = i % groups_here;
+        scale[zo + ch * d.z_sA + g] = s_scale[ch * (C::GPC + 2) + g];
+        mn[zo + ch * d.z_sA + g] = s_mn[ch * (C::GPC + 2) + g];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Any layout: one thread per output word, group statistics recomputed as needed.
+template <int BITS, typename T>
+__global__ void __launch_bounds__(128) quant_generic_kernel(const T *__restrict__ x, int32_t *__restrict__ code,
+                                                            T *__restrict__ scale, T *__restrict__ mn, QuantDims d) {
+    constexpr int E = fields_per_word(BITS);
+    constexpr int QMAX = (1 << BITS) - 1;
+    const int64_t words_per_row = d.S / E;
+    const int64_t total = d.B * d.H * d.A * words_per_row;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t row = idx / words_per_row, w = idx % words_per_row;
+    const int64_t a = row % d.A, h = (row / d.A) % d.H, b = row / (d.A * d.H);
+    const T *px = x + b * d.x_sB + h * d.x_sH + a * d.x_sA;
+    const int64_t zo = b * d.z_sB + h * d.z_sH + a * d.z_sA;
+    const int G = d.group;
+    int64_t cur = -1;
+    float lo = 0.f, sc = 0.f;
+    uint32_t word = 0;
+    for (int i = 0; i < E; ++i) {
+        const int64_t s = w * E + i, g = s / G;
+        if (g != cur) {
+            cur = g;
+            float hi = -3.402823466e+38f;
+            lo = 3.402823466e+38f;
+            for (int j = 0; j < G; ++j) {
+                const float f = to_f32<T>(px[(g * G + j) * d.x_sS]);
+                lo = fminf(lo, f); hi = fmaxf(hi, f);
+            }
+            sc = (hi - lo) / (float)QMAX;
+        }
+        if (s % G == 0) { scale[zo + g] = from_f32<T>(sc); mn[zo + g] = from_f32<T>(lo); }
+        const float n = (to_f32<T>(px[s * d.x_sS]) - lo) / sc;
+        if constexpr (BITS == 3) {
+            const int pos = (int)(s % G);   // position inside the 11-group (G == 11 enforced by the host)
+            word |= (uint32_t)round_code(n, pos < 10 ? 7 : 3) << (i < 10 ? 3 * i : 30);
+        } else {
+            word |= (uint32_t)round_code(n, QMAX) << (BITS * i);
+        }
+    }
+    code[b * d.c_sB + h * d.c_sH + a * d.c_sA + w] = (int32_t)word;
+}
+
+// ---------------------------------------------------------------------------------------------
+template <int BITS, typename T>
+static int launch_bits(const kvq_quant_args *a, const QuantDims &d, cudaStream_t st) {
+    constexpr int E = fields_per_word(BITS);
+    const T *x = static_cast<const T *>(a->x);
+    T *sc = static_cast<T *>(a->scale), *mn = static_cast<T *>(a->mn);
+    const int G = a->group;
+    const int64_t total_words = d.B * d.H * d.A * (d.S / E);
+    if (total_words == 0) return KVQ_OK;
+
+    // groups along the contiguous axis
+    const int tpg = G / E;
+    if (a->x_sS == 1 && G % E == 0 && tpg <= 32 && (tpg & (tpg - 1)) == 0) {
+        bool vec_ok = sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && d.x_sB % 8 == 0 &&
+                      d.x_sH % 8 == 0 && d.x_sA % 8 == 0;
+        const int64_t blocks = (total_words + 255) / 256;
+        quant_contig_kernel<BITS, T><<<(unsigned)blocks, 256, 0, st>>>(x, a->code, sc, mn, d, tpg, vec_ok);
+        return check_launch();
+    }
+    // groups along a strided axis, channels contiguous (keys in [T, D] order)
+    if constexpr (sizeof(T) == 2) {
+        const bool ok = a->x_sA == 1 && d.A % 128 == 0 && (reinterpret_cast<uintptr_t>(x) % 4 == 0) &&
+                        d.x_sB % 2 == 0 && d.x_sH % 2 == 0 && d.x_sS % 2 == 0 && d.B * d.H <= 65535 &&
+                        d.A / 128 <= 65535;
+        if (ok) {
+            const __half *xh = reinterpret_cast<const __half *>(x);
+            __half *sh = reinterpret_cast<__half *>(sc), *mh = reinterpret_cast<__half *>(mn);
+            const int64_t ng = d.S / G;
+#define KVQ_LAUNCH_STRIDED(GG)                                                                     \
+    {                                                                                              \
+        using C = StridedCfg<BITS, GG>;                                                            \
+        dim3 grid((unsigned)((ng + C::GPC - 1) / C::GPC), (unsigned)(d.A / 128), (unsigned)(d.B * d.H)); \
+        quant_strided_kernel<BITS, GG><<<grid, 256, 0, st>>>(xh, a->code, sh, mh, d);              \
+        return check_launch();                                                                     \
+    }
+            if constexpr (BITS == 3) {
+                if (G == 11) KVQ_LAUNCH_STRIDED(11)
+            } else {
+                if (G == 32) KVQ_LAUNCH_STRIDED(32)
+                if (G == 64) KVQ_LAUNCH_STRIDED(64)
+                if (G == 128) KVQ_LAUNCH_STRIDED(128)
+            }
+#undef KVQ_LAUNCH_STRIDED
+        }
+    }
+    const int64_t blocks = (total_words + 127) / 128;
+    quant_generic_kernel<BITS, T><<<(unsigned)blocks, 128, 0, st>>>(x, a->code, sc, mn, d);
+    return check_launch();
+}
+
+}  // namespace kvq
+
+extern "C" int kvq_quant_lastdim(const kvq_quant_args *a, kvq_stream_t stream) {
+    using namespace kvq;
+    if (!a) return KVQ_ERR_NULL;
+    if (a->bits < 1 || a->bits > 4) return KVQ_ERR_BITS;
+    if (a->B < 0 || a->H < 0 || a->A < 0 || a->S < 0) return KVQ_ERR_SHAPE;
+    if (a->bits == 3) {
+        if (a->group != 11) return KVQ_ERR_GROUP3;
+        if (a->S % 11 != 0) return KVQ_ERR_DIV11;
+    } else {
+        if (a->group <= 0 || a->S % a->group != 0) return KVQ_ERR_DIVGROUP;
+        if (a->S % (32 / a->bits) != 0) return KVQ_ERR_DIVWORD;
+    }
+    if (a->B * a->H * a->A * a->S == 0) return KVQ_OK;
+    if (!a->x || !a->code || !a->scale || !a->mn) return KVQ_ERR_NULL;
+    QuantDims d{a->B, a->H, a->A, a->S, a->x_sB, a->x_sH, a->x_sA, a->x_sS, a->c_sB, a->c_sH, a->c_sA,
+                a->z_sB, a->z_sH, a->z_sA, a->group};
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define KVQ_DISPATCH(BITS)                                                             \
+    case BITS:                                                                         \
+        return a->x_is_f32 ? launch_bits<BITS, float>(a, d, st) : launch_bits<BITS, __half>(a, d, st);
+    switch (a->bits) {
+        KVQ_DISPATCH(1)
+        KVQ_DISPATCH(2)
+        KVQ_DISPATCH(3)
+        KVQ_DISPATCH(4)
+    }
+#undef KVQ_DISPATCH
+    return KVQ_ERR_BITS;
+}

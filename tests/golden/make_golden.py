@@ -1,0 +1,159 @@
+"""Generate tests/golden/ref_vectors.npz by running the upstream CUDA extension on a GPU.
+
+Run on a machine with a B200 after ``python oracle/build_ref.py`` has produced the two builds of
+the unmodified upstream sources in oracle/_ref/:
+
+    python tests/golden/make_golden.py --out tests/golden/ref_vectors.npz
+
+``KVmix_ref_ieee`` (upstream sources, no --use_fast_math) supplies the vectors; ``KVmix_ref_fast``
+(upstream's own flags) is run on the same inputs and the number of code words that differ from the
+IEEE build is recorded (approximate division flips rounding ties).  A larger statistical run
+(4 Mi values per bit width) records tie-flip rates in ``ref_report.json``.  Inputs are seeded
+synthetic tensors: N(0,1) with a few outlier channels, constant groups and exact .5 ties.
+"""
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, os.path.join(ROOT, "oracle", "_ref"))
+sys.path.insert(0, ROOT)
+
+
+def fpi(bits):
+    return 11 if bits == 3 else 32 // bits
+
+
+def make_input(rng, shape, special=True):
+    x = rng.standard_normal(shape).astype(np.float32)
+    x[..., 1, :] *= 8.0                       # an outlier row
+    if special:
+        flat = x.reshape(-1, shape[-1])
+        flat[0, :] = 0.75                     # constant groups: scale 0
+        # exact ties: integers k and k + 0.5 in a group whose min is 0 and max is 2^b - 1 times 1.0
+        n = shape[-1]
+        flat[2, :] = (np.arange(n) % 16).astype(np.float32) * 0.5
+    return x.astype(np.float16)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default=os.path.join(HERE, "ref_vectors.npz"))
+    ap.add_argument("--report", default=None)
+    a = ap.parse_args()
+    import KVmix_ref_fast as RF
+    import KVmix_ref_ieee as RI
+    import oracle
+
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(20251125)
+    out = {}
+    report = {"cases": {}, "tie_stats": {}}
+    t = lambda a_: torch.from_numpy(a_).to(dev)
+    n_ = lambda t_: t_.detach().cpu().numpy()
+
+    # ---- quantize_pack_last_dim_cuda -------------------------------------------------------------
+    for bits, G in [(4, 32), (2, 32), (1, 32), (3, 11), (4, 64), (2, 128)]:
+        f = fpi(bits)
+        shapes = {"k": (1, 2, 128, 66 if bits == 3 else 2 * max(G, f)),         # [B,H,D,T]: per-channel groups
+                  "v": (1, 2, 12, 132 if bits == 3 else 128)}                    # [B,H,T,D]: per-token groups
+        for style, shp in shapes.items():
+            x = make_input(rng, shp)
+            key = f"quant_{style}_b{bits}_g{G}"
+            ci, si, mi = RI.quantize_pack_last_dim_cuda(t(x), G, bits)
+            cf, sf, mf = RF.quantize_pack_last_dim_cuda(t(x), G, bits)
+            out[key + "_x"] = x
+            out[key + "_code"], out[key + "_scale"], out[key + "_mn"] = n_(ci), n_(si), n_(mi)
+            co, so, mo = oracle.quantize_pack_last_dim(x, G, bits)
+            report["cases"][key] = {
+                "words": int(ci.numel()),
+                "fast_vs_ieee_word_diffs": int((cf != ci).sum().item()),
+                "oracle_vs_ieee_word_diffs": int((co != n_(ci)).sum()),
+                "oracle_scale_equal": bool((so == n_(si)).all()), "oracle_mn_equal": bool((mo == n_(mi)).all()),
+            }
+    # fp32 input keeps fp32 scale/min
+    x32 = rng.standard_normal((1, 1, 16, 64)).astype(np.float32)
+    c, s, m = RI.quantize_pack_last_dim_cuda(t(x32), 32, 4)
+    out["quant_f32_b4_g32_x"], out["quant_f32_b4_g32_code"] = x32, n_(c)
+    out["quant_f32_b4_g32_scale"], out["quant_f32_b4_g32_mn"] = n_(s), n_(m)
+
+    # ---- quantized_gemm ---------------------------------------------------------------------------
+    for bits, G in [(4, 32), (2, 32), (1, 32), (3, 11)]:
+        f = fpi(bits)
+        # q.K^T : K = 128 channels, N = tokens
+        T = 66 if bits == 3 else 128
+        kt = make_input(rng, (1, 2, 128, T), special=False)
+        code, sc, mn = RI.quantize_pack_last_dim_cuda(t(kt), G, bits)
+        for nh in (2, 4):
+            q = rng.standard_normal((1, nh, 1, 128)).astype(np.float16)
+            o = RI.quantized_gemm(G, t(q), code, sc, mn, bits)
+            torch.cuda.synchronize()
+            key = f"gemv_qk_b{bits}_g{G}_nh{nh}"
+            out[key + "_q"], out[key + "_out"] = q, n_(o)
+            if nh == 2:
+                out[key + "_code"], out[key + "_scale"], out[key + "_mn"] = n_(code), n_(sc), n_(mn)
+            oo = oracle.quantized_gemm(G, q, n_(code), n_(sc), n_(mn), bits)
+            report["cases"][key] = {"max_abs_diff_oracle": float(np.abs(oo.astype(np.float32) - n_(o).astype(np.float32)).max()),
+                                    "bit_equal": bool((oo.view(np.uint16) == n_(o).view(np.uint16)).all())}
+        # p.V : K = tokens, N = 128 channels (3-bit values need D % 11 == 0 upstream: use D = 132)
+        D = 132 if bits == 3 else 128
+        Tv = 160
+        v = make_input(rng, (1, 2, Tv, D), special=False)
+        code, sc, mn = RI.quantize_pack_last_dim_cuda(t(v), G, bits)
+        p = np.abs(rng.standard_normal((1, 2, 1, Tv))).astype(np.float16) / Tv
+        o = RI.quantized_gemm(G, t(p), code, sc, mn, bits)
+        torch.cuda.synchronize()
+        key = f"gemv_pv_b{bits}_g{G}"
+        out[key + "_p"], out[key + "_out"] = p, n_(o)
+        out[key + "_code"], out[key + "_scale"], out[key + "_mn"] = n_(code), n_(sc), n_(mn)
+        oo = oracle.quantized_gemm(G, p, n_(code), n_(sc), n_(mn), bits)
+        report["cases"][key] = {"max_abs_diff_oracle": float(np.abs(oo.astype(np.float32) - n_(o).astype(np.float32)).max()),
+                                "bit_equal": bool((oo.view(np.uint16) == n_(o).view(np.uint16)).all())}
+
+    # ---- append forms -----------------------------------------------------------------------------
+    for bits, G in [(4, 32), (2, 32), (1, 32)]:
+        xk0 = make_input(rng, (1, 2, 128, 64), special=False)
+        xk1 = make_input(rng, (1, 2, 128, 32), special=False)
+        c0, s0, m0 = RI.quantize_pack_last_dim_cuda(t(xk0), G, bits)
+        c1, s1, m1 = RI.process_key_quantization_cuda(t(xk1), c0, s0, m0, G, bits)
+        key = f"appendk_b{bits}_g{G}"
+        out[key + "_x0"], out[key + "_x1"] = xk0, xk1
+        out[key + "_code"], out[key + "_scale"], out[key + "_mn"] = n_(c1), n_(s1), n_(m1)
+        xv0 = make_input(rng, (1, 2, 8, 128), special=False)
+        xv1 = make_input(rng, (1, 2, 4, 128), special=False)
+        c0, s0, m0 = RI.quantize_pack_last_dim_cuda(t(xv0), G, bits)
+        c1, s1, m1 = RI.process_value_quantization_cuda(t(xv1), c0, s0, m0, G, bits)
+        key = f"appendv_b{bits}_g{G}"
+        out[key + "_x0"], out[key + "_x1"] = xv0, xv1
+        out[key + "_code"], out[key + "_scale"], out[key + "_mn"] = n_(c1), n_(s1), n_(m1)
+
+    # ---- tie-flip statistics (report only) --------------------------------------------------------
+    big = np.random.default_rng(7).standard_normal((4, 32, 128, 264)).astype(np.float16)   # 4.3 Mi values
+    for bits, G in [(4, 32), (2, 32), (1, 32), (3, 11)]:
+        S = 264 if bits == 3 else 256
+        xb = np.ascontiguousarray(big[..., :S])
+        ci, si, mi = RI.quantize_pack_last_dim_cuda(t(xb), G, bits)
+        cf, sf, mf = RF.quantize_pack_last_dim_cuda(t(xb), G, bits)
+        co, so, mo = oracle.quantize_pack_last_dim(xb, G, bits)
+        report["tie_stats"][f"b{bits}_g{G}"] = {
+            "values": int(xb.size), "words": int(ci.numel()),
+            "fast_vs_ieee_word_diffs": int((cf != ci).sum().item()),
+            "oracle_vs_ieee_word_diffs": int((co != n_(ci)).sum()),
+            "oracle_vs_fast_word_diffs": int((co != n_(cf)).sum()),
+            "oracle_scale_equal_ieee": bool((so == n_(si)).all()),
+        }
+    np.savez_compressed(a.out, **out)
+    rep = a.report or os.path.join(os.path.dirname(a.out), "ref_report.json")
+    with open(rep, "w") as fjs:
+        json.dump(report, fjs, indent=1, sort_keys=True)
+    print(json.dumps(report, indent=1, sort_keys=True))
+    print("wrote", a.out, os.path.getsize(a.out), "bytes")
+
+
+if __name__ == "__main__":
+    main()

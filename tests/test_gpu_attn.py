@@ -1,0 +1,156 @@
+"""GPU parity of the fused decode attention and of the preallocated cache against the CPU oracle
+(upstream rounding points R1-R6), within 2e-3 relative per (batch, head) row."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle.glue import RefLayerCache
+from util import assert_attn_close, make_kv, make_q
+
+pytestmark = pytest.mark.gpu
+
+
+def _t(a, dev):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def _attend_gpu(c, q, dev, **kw):
+    import kvmix_b200 as kv
+    return kv.decode_attention(_t(q, dev), _t(c.kcode, dev), _t(c.kscale, dev), _t(c.kmn, dev), _t(c.kfull, dev),
+                               _t(c.vcode, dev), _t(c.vscale, dev), _t(c.vmn, dev), _t(c.vfull, dev), c.k_bits,
+                               c.k_group, c.v_bits, c.v_group, **kw).cpu().numpy()
+
+
+def test_config1_micro(cuda):
+    """Batch 1, 32 heads, ctx 1024, K4 per-channel / V2 per-token, group 32, fp16 window 128."""
+    import kvmix_b200 as kv
+    k, v = make_kv(0, 1, 32, 1024)
+    q = make_q(0, 1, 32)
+    ref = RefLayerCache(4, 2, 32, residual_length=128)
+    ref.prefill(k, v)
+    assert ref.tkq == 896 and ref.tvq == 896
+    # packed codes bit-exact, scale/zero exact
+    kc, ks, km = kv.quantize_pack_last_dim_cuda(_t(k, cuda)[:, :, :896].transpose(2, 3), 32, 4)
+    vc, vs, vm = kv.quantize_pack_last_dim_cuda(_t(v, cuda)[:, :, :896], 32, 2)
+    assert (kc.cpu().numpy() == ref.kcode).all() and (vc.cpu().numpy() == ref.vcode).all()
+    for g, w in [(ks, ref.kscale), (km, ref.kmn), (vs, ref.vscale), (vm, ref.vmn)]:
+        assert (g.cpu().numpy().view(np.uint16) == w.view(np.uint16)).all()
+    got = _attend_gpu(ref, q, cuda)
+    assert_attn_close(got, ref.attend(q, ref_rounding=True))
+    assert_attn_close(got, ref.attend(q, ref_rounding=False))
+
+
+@pytest.mark.parametrize("kb,vb,G", [(4, 4, 32), (3, 2, 32), (2, 2, 32), (2, 1, 64), (4, 4, 64), (1, 2, 32), (3, 4, 128),
+                                     (4, 2, 128), (1, 1, 128)])
+@pytest.mark.parametrize("nh,hkv", [(4, 4), (8, 2)])
+def test_bit_widths_groups_gqa(cuda, kb, vb, G, nh, hkv):
+    T = 1500
+    k, v = make_kv(kb * 10 + vb, 2, hkv, T)
+    q = make_q(kb, 2, nh)
+    ref = RefLayerCache(kb, vb, G, residual_length=128)
+    ref.prefill(k, v)
+    got = _attend_gpu(ref, q, cuda)
+    assert_attn_close(got, ref.attend(q, ref_rounding=True))
+
+
+def test_independent_boundaries_ratio_policy(cuda):
+    """Upstream's ratio policy gives different K and V split points (group 11 vs 32, ratio 0.2 vs 0.3)."""
+    k, v = make_kv(11, 1, 4, 777)
+    q = make_q(11, 1, 4)
+    ref = RefLayerCache(3, 4, 32, k_residual_ratio=0.2, v_residual_ratio=0.3)
+    ref.prefill(k, v)
+    assert ref.tkq != ref.tvq
+    assert_attn_close(_attend_gpu(ref, q, cuda), ref.attend(q))
+
+
+def test_edge_cases_no_packed_part_and_tiny_context(cuda):
+    for T in (1, 5, 31, 127):
+        k, v = make_kv(T, 1, 2, T)
+        q = make_q(T, 1, 4)
+        ref = RefLayerCache(4, 2, 32, residual_length=128)
+        ref.prefill(k, v)
+        assert ref.kcode is None and ref.vcode is None
+        assert_attn_close(_attend_gpu(ref, q, cuda), ref.attend(q))
+
+
+def test_fully_packed_keys_zero_tail(cuda):
+    """residual_length 0: every key is packed when T is a group multiple."""
+    k, v = make_kv(2, 1, 2, 256)
+    q = make_q(2, 1, 2)
+    ref = RefLayerCache(2, 4, 32, residual_length=0)
+    ref.prefill(k, v)
+    assert ref.kfull.shape[2] == 0 and ref.tkq == 256
+    assert_attn_close(_attend_gpu(ref, q, cuda), ref.attend(q))
+
+
+def test_split_merge_long_context_is_deterministic(cuda):
+    """Few heads and a long context force many splits and the last-CTA merge."""
+    T = 20000
+    k, v = make_kv(5, 1, 2, T)
+    q = make_q(5, 1, 8)
+    ref = RefLayerCache(3, 2, 128, residual_length=256)
+    ref.prefill(k, v)
+    a = _attend_gpu(ref, q, cuda)
+    b = _attend_gpu(ref, q, cuda)
+    assert (a.view(np.uint16) == b.view(np.uint16)).all()
+    assert_attn_close(a, ref.attend(q))
+
+
+@pytest.mark.parametrize("policy", ["window", "ratio"])
+@pytest.mark.parametrize("kb,vb,G", [(4, 2, 32), (3, 2, 32), (2, 1, 64)])
+def test_cache_decode_loop_matches_glue(cuda, policy, kb, vb, G):
+    """Prefill + 80 decode steps: the preallocated ring cache and upstream's cat-based protocol hold the
+    same tokens in the same form at every step, and attention matches."""
+    import kvmix_b200 as kv
+    B, hkv, nh, L, steps = 2, 2, 4, 300, 80
+    k, v = make_kv(21, B, hkv, L + steps)
+    pol = dict(residual_length=128) if policy == "window" else dict(k_residual_ratio=0.2, v_residual_ratio=0.1)
+    ref = RefLayerCache(kb, vb, G, **pol)
+    dut = kv.KVmixLayerCache(B, hkv, 128, L + steps, kb, vb, G, device=cuda, **pol)
+    kt, vt = _t(k, cuda), _t(v, cuda)
+    ref.prefill(k[:, :, :L], v[:, :, :L])
+    dut.prefill(kt[:, :, :L], vt[:, :, :L])
+    for i in range(steps):
+        t = L + i
+        q = make_q(t, B, nh)
+        want = ref.decode_step(q, k[:, :, t:t + 1], v[:, :, t:t + 1])
+        got = dut.decode_step(_t(q, cuda), kt[:, :, t:t + 1], vt[:, :, t:t + 1]).cpu().numpy()
+        assert dut.tkq == ref.tkq and dut.tvq == ref.tvq and dut.kv_seq_len == ref.kv_seq_len
+        assert_attn_close(got, want)
+    tup = dut.as_tuple()
+    for g, w in zip(tup[:8], [ref.kcode, ref.kfull, ref.kscale, ref.kmn, ref.vcode, ref.vfull, ref.vscale, ref.vmn]):
+        g = g.cpu().numpy()
+        assert g.shape == w.shape
+        assert (g.view(np.uint16) == w.view(np.uint16)).all() if g.dtype == np.float16 else (g == w).all()
+
+
+def test_nine_tuple_protocol_drop_in(cuda):
+    """attention_step keeps upstream's past_key_value 9-tuple contract (prefill then decode)."""
+    import kvmix_b200 as kv
+    B, hkv, nh, L = 1, 2, 8, 200
+    k, v = make_kv(31, B, hkv, L + 40)
+    kt, vt = _t(k, cuda), _t(v, cuda)
+    ref = RefLayerCache(2, 2, 32, k_residual_ratio=0.2, v_residual_ratio=0.2)
+    ref.prefill(k[:, :, :L], v[:, :, :L])
+    qp = torch.randn((B, nh, L, 128), dtype=torch.float16, device=cuda)
+    _, past = kv.attention_step(qp, kt[:, :, :L], vt[:, :, :L], None, 2, 2, 32, 0.2, 0.2)
+    assert past[8] == L
+    for i in range(40):
+        t = L + i
+        q = make_q(t, B, nh)
+        want = ref.decode_step(q, k[:, :, t:t + 1], v[:, :, t:t + 1])
+        got, past = kv.attention_step(_t(q, cuda), kt[:, :, t:t + 1], vt[:, :, t:t + 1], past, 2, 2, 32, 0.2, 0.2)
+        assert past[8] == t + 1 and past[0].shape[3] * 16 == ref.tkq
+        assert_attn_close(got.cpu().numpy(), want)
+
+
+def test_attention_argument_errors(cuda):
+    import kvmix_b200 as kv
+    z = lambda *s, dt=torch.float16: torch.zeros(s, dtype=dt, device=cuda)
+    with pytest.raises(RuntimeError, match="token counts"):
+        kv.decode_attention(z(1, 2, 1, 128), None, None, None, z(1, 2, 5, 128), None, None, None, z(1, 2, 6, 128),
+                            4, 32, 4, 32)
+    with pytest.raises(RuntimeError, match="not supported"):
+        kv.decode_attention(z(1, 2, 1, 64), None, None, None, z(1, 2, 5, 64), None, None, None, z(1, 2, 5, 64),
+                            4, 32, 4, 32)
