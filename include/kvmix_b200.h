@@ -70,6 +70,10 @@ int kvq_features_per_int(int bits);
  * x_is_f32 = 0: x, scale, mn are fp16;  1: they are fp32.
  * Rules (same as upstream): bits == 3 needs group == 11 and S % 11 == 0; otherwise
  * S % group == 0 and S % (32/bits) == 0.
+ * Codes always come from the true fp32 quotient (x-mn)/((max-min)/(2^b-1)).  The *stored* scale is
+ *   scale_by_division = 0: (max-min) * fl32(1/(2^b-1)), what quantize_pack_last_dim_cuda returns
+ *       (its torch-side "tensor / scalar" at :711 is evaluated as a multiplication by the reciprocal);
+ *   scale_by_division = 1: (max-min) / (2^b-1), what the upstream append kernels store (:51-53, :232-234).
  */
 typedef struct {
     const void *x;
@@ -77,6 +81,7 @@ typedef struct {
     int64_t B, H, A, S;
     int64_t x_sB, x_sH, x_sA, x_sS;
     int32_t group, bits;
+    int32_t scale_by_division;
     int32_t *code;
     int64_t c_sB, c_sH, c_sA;
     void *scale;

@@ -44,7 +44,13 @@ struct QuantDims {
     int64_t c_sB, c_sH, c_sA;
     int64_t z_sB, z_sH, z_sA;
     int group;
+    int by_div;   // stored scale: 1 = (mx-mn)/qmax, 0 = (mx-mn) * fl32(1/qmax)
 };
+
+template <int QMAX>
+__device__ __forceinline__ float stored_scale(float range, float quotient, int by_div) {
+    return by_div ? quotient : __fmul_rn(range, 1.0f / (float)QMAX);
+}
 
 // ---------------------------------------------------------------------------------------------
 // Contiguous groups.  E = fields per word elements per thread, TPG = group / E threads per group.
@@ -108,7 +114,7 @@ __global__ void __launch_bounds__(256) quant_contig_kernel(const T *__restrict__
         code[b * d.c_sB + h * d.c_sH + a * d.c_sA + w] = (int32_t)word;
         if ((w % tpg) == 0) {
             const int64_t zo = b * d.z_sB + h * d.z_sH + a * d.z_sA + w / tpg;
-            scale[zo] = from_f32<T>(sc);
+            scale[zo] = from_f32<T>(stored_scale<QMAX>(hi - lo, sc, d.by_div));
             mn[zo] = from_f32<T>(lo);
         }
     }
@@ -180,8 +186,8 @@ __global__ void __launch_bounds__(256) quant_strided_kernel(const __half *__rest
             s_code[(2 * pair) * C::WPAD + g * C::WPG + w] = (int32_t)w0;
             s_code[(2 * pair + 1) * C::WPAD + g * C::WPG + w] = (int32_t)w1;
         }
-        s_scale[(2 * pair) * (C::GPC + 2) + g] = __float2half_rn(sc0);
-        s_scale[(2 * pair + 1) * (C::GPC + 2) + g] = __float2half_rn(sc1);
+        s_scale[(2 * pair) * (C::GPC + 2) + g] = __float2half_rn(stored_scale<QMAX>(hi0 - lo0, sc0, d.by_div));
+        s_scale[(2 * pair + 1) * (C::GPC + 2) + g] = __float2half_rn(stored_scale<QMAX>(hi1 - lo1, sc1, d.by_div));
         s_mn[(2 * pair) * (C::GPC + 2) + g] = __float2half_rn(lo0);
         s_mn[(2 * pair + 1) * (C::GPC + 2) + g] = __float2half_rn(lo1);
     }
@@ -217,7 +223,7 @@ __global__ void __launch_bounds__(128) quant_generic_kernel(const T *__restrict_
     const int64_t zo = b * d.z_sB + h * d.z_sH + a * d.z_sA;
     const int G = d.group;
     int64_t cur = -1;
-    float lo = 0.f, sc = 0.f;
+    float lo = 0.f, sc = 0.f, range = 0.f;
     uint32_t word = 0;
     for (int i = 0; i < E; ++i) {
         const int64_t s = w * E + i, g = s / G;
@@ -229,9 +235,13 @@ __global__ void __launch_bounds__(128) quant_generic_kernel(const T *__restrict_
                 const float f = to_f32<T>(px[(g * G + j) * d.x_sS]);
                 lo = fminf(lo, f); hi = fmaxf(hi, f);
             }
-            sc = (hi - lo) / (float)QMAX;
+            range = hi - lo;
+            sc = range / (float)QMAX;
         }
-        if (s % G == 0) { scale[zo + g] = from_f32<T>(sc); mn[zo + g] = from_f32<T>(lo); }
+        if (s % G == 0) {
+            scale[zo + g] = from_f32<T>(stored_scale<QMAX>(range, sc, d.by_div));
+            mn[zo + g] = from_f32<T>(lo);
+        }
         const float n = (to_f32<T>(px[s * d.x_sS]) - lo) / sc;
         if constexpr (BITS == 3) {
             const int pos = (int)(s % G);   // position inside the 11-group (G == 11 enforced by the host)
@@ -310,7 +320,7 @@ extern "C" int kvq_quant_lastdim(const kvq_quant_args *a, kvq_stream_t stream) {
     if (a->B * a->H * a->A * a->S == 0) return KVQ_OK;
     if (!a->x || !a->code || !a->scale || !a->mn) return KVQ_ERR_NULL;
     QuantDims d{a->B, a->H, a->A, a->S, a->x_sB, a->x_sH, a->x_sA, a->x_sS, a->c_sB, a->c_sH, a->c_sA,
-                a->z_sB, a->z_sH, a->z_sA, a->group};
+                a->z_sB, a->z_sH, a->z_sA, a->group, a->scale_by_division ? 1 : 0};
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define KVQ_DISPATCH(BITS)                                                             \
     case BITS:                                                                         \

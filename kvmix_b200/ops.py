@@ -53,11 +53,13 @@ def _check_quant_rules(S, group_length, quant_bits):
             check(-5)
 
 
-def quantize_into(x, group_length, quant_bits, code, scale, mn):
+def quantize_into(x, group_length, quant_bits, code, scale, mn, scale_by_division=False):
     """Quantize 4-D ``x`` (any strides) along its last dim into preallocated views.
 
     ``code`` [B,H,A,S/fpi] int32, ``scale``/``mn`` [B,H,A,S/G] (dtype of x); their last dim must be
     contiguous, other strides are free, so they may be slices of a larger cache.
+    ``scale_by_division`` selects how the stored scale is rounded (see include/kvmix_b200.h): False
+    reproduces quantize_pack_last_dim_cuda, True the upstream append kernels.
     """
     _need_cuda(x, code, scale, mn)
     if x.dim() != 4:
@@ -75,7 +77,7 @@ def quantize_into(x, group_length, quant_bits, code, scale, mn):
         return
     assert code.stride(3) == 1 and scale.stride(3) == 1
     a = QuantArgs(x.data_ptr(), int(x.dtype == torch.float32), B, H, A, S, x.stride(0), x.stride(1), x.stride(2),
-                  x.stride(3), group_length, quant_bits, code.data_ptr(), code.stride(0), code.stride(1),
+                  x.stride(3), group_length, quant_bits, int(bool(scale_by_division)), code.data_ptr(), code.stride(0), code.stride(1),
                   code.stride(2), scale.data_ptr(), mn.data_ptr(), scale.stride(0), scale.stride(1),
                   scale.stride(2))
     check(_lib.lib().kvq_quant_lastdim(C.byref(a), _stream()))
@@ -175,7 +177,8 @@ def process_key_quantization_cuda(input_tensor, previous_code, previous_scale, p
     code[..., :old_w].copy_(previous_code)
     scale[..., :old_g].copy_(previous_scale)
     mn[..., :old_g].copy_(previous_min)
-    quantize_into(input_tensor, group_length, quant_bits, code[..., old_w:], scale[..., old_g:], mn[..., old_g:])
+    quantize_into(input_tensor, group_length, quant_bits, code[..., old_w:], scale[..., old_g:], mn[..., old_g:],
+                  scale_by_division=True)
     return code, scale, mn
 
 
@@ -203,7 +206,8 @@ def process_value_quantization_cuda(input_tensor, previous_code, previous_scale,
     code[:, :, :Told].copy_(previous_code)
     scale[:, :, :Told].copy_(previous_scale)
     mn[:, :, :Told].copy_(previous_min)
-    quantize_into(input_tensor, group_length, quant_bits, code[:, :, Told:], scale[:, :, Told:], mn[:, :, Told:])
+    quantize_into(input_tensor, group_length, quant_bits, code[:, :, Told:], scale[:, :, Told:], mn[:, :, Told:],
+                  scale_by_division=True)
     return code, scale, mn
 
 

@@ -164,7 +164,7 @@ def decode_attention(q, kcode, kscale, kmn, kfull, vcode, vscale, vmn, vfull, k_
     out = np.empty((B, nh, 1, D), np.float16)
     i64 = ctypes.c_int64
     rc = lib().orc_decode_attn(*[_p(a) for a in arrs], i64(B), i64(nh), i64(Hkv), i64(D), i64(Tkq), i64(Rk),
-                               i64(Tvq), i64(Rv), k_bits, k_group, v_bits, v_group, int(bool(ref_rounding)),
+                               i64(Tvq), i64(Rv), k_bits, k_group, v_bits, v_group, (7 if ref_rounding is True else int(ref_rounding)),
                                _p(out))
     _check(rc)
     return out

@@ -94,10 +94,15 @@ static void quant_row(const float *x, int64_t S, int G, int bits, int32_t *code,
 /*
  * quantize_pack_last_dim_cuda on an fp16 tensor viewed as [rows, S] (quantization_cuda.cu:631-721):
  * the fp16 input is widened to fp32 (:641-642), quantized, and scale = (max-min)/(2^b-1) is
- * recomputed in fp32 (:711) and then narrowed to fp16 together with min (:715-718).
+ * recomputed on the torch side in fp32 (:711) and then narrowed to fp16 together with min
+ * (:715-718).  torch evaluates "tensor / host scalar" as tensor * (1/scalar) in the tensor's
+ * dtype, so the returned scale is (max-min) * fl32(1/(2^b-1)) -- not the true quotient the
+ * kernel used for the codes (:570).  The vectors from the real extension pin this (every fp32
+ * scale of the fp32-input case differs otherwise).  The append forms below store the in-kernel
+ * quotient instead (:51-53, :150-152, :232-234), hence the scale_by_division switch.
  */
-int orc_quant_lastdim_f16(const h16 *x, int64_t rows, int64_t S, int G, int bits, int32_t *code,
-                          h16 *scale, h16 *mn) {
+static int quant_lastdim_f16(const h16 *x, int64_t rows, int64_t S, int G, int bits, int32_t *code,
+                             h16 *scale, h16 *mn, int scale_by_division) {
     int rc = orc_quant_check(S, G, bits);
     if (rc) return rc;
     const int fpi = orc_features_per_int(bits);
@@ -114,13 +119,19 @@ int orc_quant_lastdim_f16(const h16 *x, int64_t rows, int64_t S, int G, int bits
             for (int64_t i = 0; i < S; ++i) xf[i] = h2f(x[r * S + i]);
             quant_row(xf, S, G, bits, code + r * nw, mnf, mxf, tmp);
             for (int64_t g = 0; g < ng; ++g) {
-                scale[r * ng + g] = f2h((mxf[g] - mnf[g]) / qmax);
+                scale[r * ng + g] = scale_by_division ? f2h((mxf[g] - mnf[g]) / qmax)
+                                                      : f2h((mxf[g] - mnf[g]) * (1.0f / qmax));
                 mn[r * ng + g] = f2h(mnf[g]);
             }
         }
         free(xf); free(mnf); free(tmp);
     }
     return 0;
+}
+
+int orc_quant_lastdim_f16(const h16 *x, int64_t rows, int64_t S, int G, int bits, int32_t *code,
+                          h16 *scale, h16 *mn) {
+    return quant_lastdim_f16(x, rows, S, G, bits, code, scale, mn, 0);
 }
 
 /* Same for an fp32 tensor: scale and min stay fp32 (quantization_cuda.cu:641,715). */
@@ -138,7 +149,7 @@ int orc_quant_lastdim_f32(const float *x, int64_t rows, int64_t S, int G, int bi
 #pragma omp for schedule(static)
         for (int64_t r = 0; r < rows; ++r) {
             quant_row(x + r * S, S, G, bits, code + r * nw, mn + r * ng, mxf, tmp);
-            for (int64_t g = 0; g < ng; ++g) scale[r * ng + g] = (mxf[g] - mn[r * ng + g]) / qmax;
+            for (int64_t g = 0; g < ng; ++g) scale[r * ng + g] = (mxf[g] - mn[r * ng + g]) * (1.0f / qmax);
         }
         free(mxf); free(tmp);
     }
@@ -247,7 +258,7 @@ int orc_append_k_f16(const h16 *xnew, int64_t rows, int64_t Tn, const int32_t *p
     int32_t *c_new = (int32_t *)malloc(sizeof(int32_t) * (size_t)(rows * nw + 1));
     h16 *s_new = (h16 *)malloc(sizeof(h16) * (size_t)(rows * ng + 1));
     h16 *m_new = (h16 *)malloc(sizeof(h16) * (size_t)(rows * ng + 1));
-    int rc = orc_quant_lastdim_f16(xnew, rows, Tn, G, bits, c_new, s_new, m_new);
+    int rc = quant_lastdim_f16(xnew, rows, Tn, G, bits, c_new, s_new, m_new, 1);
     if (rc == 0) {
         for (int64_t r = 0; r < rows; ++r) {
             memcpy(code + r * (old_w + nw), prev_code + r * old_w, sizeof(int32_t) * (size_t)old_w);
@@ -277,8 +288,8 @@ int orc_append_v_f16(const h16 *xnew, int64_t bh, int64_t Tn, int64_t D, const i
         memcpy(code + r * (Told + Tn) * wpt, prev_code + r * Told * wpt, sizeof(int32_t) * (size_t)(Told * wpt));
         memcpy(scale + r * (Told + Tn) * gpt, prev_scale + r * Told * gpt, sizeof(h16) * (size_t)(Told * gpt));
         memcpy(mn + r * (Told + Tn) * gpt, prev_mn + r * Told * gpt, sizeof(h16) * (size_t)(Told * gpt));
-        rc = orc_quant_lastdim_f16(xnew + r * Tn * D, Tn, D, G, bits, code + (r * (Told + Tn) + Told) * wpt,
-                                   scale + (r * (Told + Tn) + Told) * gpt, mn + (r * (Told + Tn) + Told) * gpt);
+        rc = quant_lastdim_f16(xnew + r * Tn * D, Tn, D, G, bits, code + (r * (Told + Tn) + Told) * wpt,
+                               scale + (r * (Told + Tn) + Told) * gpt, mn + (r * (Told + Tn) + Told) * gpt, 1);
         if (rc) return rc;
     }
     return 0;
@@ -294,7 +305,8 @@ int orc_append_v_f16(const h16 *xnew, int64_t bh, int64_t Tn, int64_t D, const i
  *   R4 softmax in fp32, probabilities -> fp16 (:194)
  *   R5 p.Vq -> fp16 (GEMV) and p.Vfull -> fp16 (:205-210)
  *   R6 fp16 sum of the two (:211)
- * With ref_rounding == 0 nothing is narrowed before the final fp16 store (fp32-accumulate mode).
+ * ref_rounding is a bit mask: 1 = R1+R2, 2 = R4, 4 = R5+R6 (7 = upstream).  With 0 nothing is
+ * narrowed before the final fp16 store (fp32-accumulate mode).
  * GQA: query head h reads kv head h / (nh / nh_kv), which is what repeat_kv_quant
  * (modeling_llama_KVmix.py:19-28) materialises.  The quantized products use plain fp32
  * accumulation here (order differs from the GEMV tree above by rounding noise only).
@@ -341,12 +353,12 @@ int orc_decode_attn(const h16 *q, const int32_t *kcode, const h16 *kscale, const
                     }
                 }
             }
-            if (ref_rounding) for (int64_t t = 0; t < Tkq; ++t) sc[t] = h2f(f2h(sc[t]));          /* R1 */
+            if (ref_rounding & 1) for (int64_t t = 0; t < Tkq; ++t) sc[t] = h2f(f2h(sc[t]));      /* R1 */
             for (int64_t r = 0; r < Rk; ++r) {
                 const h16 *kr = kfull + (kv * Rk + r) * D;
                 float a = 0.0f;
                 for (int64_t d = 0; d < D; ++d) a = fmaf(h2f(qv[d]), h2f(kr[d]), a);
-                sc[Tkq + r] = ref_rounding ? h2f(f2h(a)) : a;                                      /* R2 */
+                sc[Tkq + r] = (ref_rounding & 1) ? h2f(f2h(a)) : a;                                /* R2 */
             }
             float mx = -FLT_MAX;
             for (int64_t t = 0; t < T; ++t) { sc[t] = sc[t] / sqrtf((float)D); mx = fmaxf(mx, sc[t]); } /* R3 */
@@ -354,7 +366,7 @@ int orc_decode_attn(const h16 *q, const int32_t *kcode, const h16 *kscale, const
             for (int64_t t = 0; t < T; ++t) { sc[t] = expf(sc[t] - mx); sum += sc[t]; }
             for (int64_t t = 0; t < T; ++t) {
                 sc[t] = sc[t] / sum;
-                if (ref_rounding) sc[t] = h2f(f2h(sc[t]));                                         /* R4 */
+                if (ref_rounding & 2) sc[t] = h2f(f2h(sc[t]));                                     /* R4 */
             }
             for (int64_t d = 0; d < D; ++d) { acc_q[d] = 0.0f; acc_f[d] = 0.0f; }
             for (int64_t t = 0; t < Tvq; ++t) {
@@ -378,7 +390,7 @@ int orc_decode_attn(const h16 *q, const int32_t *kcode, const h16 *kscale, const
                 for (int64_t d = 0; d < D; ++d) acc_f[d] = fmaf(p, h2f(vr[d]), acc_f[d]);
             }
             for (int64_t d = 0; d < D; ++d) {
-                if (ref_rounding) {
+                if (ref_rounding & 4) {
                     float a = Tvq ? h2f(f2h(acc_q[d])) : 0.0f, f = h2f(f2h(acc_f[d]));            /* R5 */
                     out[s * D + d] = Tvq ? f2h(a + f) : f2h(acc_f[d]);                              /* R6 */
                 } else {

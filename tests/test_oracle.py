@@ -30,7 +30,8 @@ def np_quant(x, G, bits):
         w = sum(qw[..., i] << (bits * i) for i in range(fpi))
     w = (w & 0xFFFFFFFF).astype(np.uint32).view(np.int32)
     shp = x.shape[:-1]
-    return (w.reshape(shp + (S // fpi,)), sc.astype(x.dtype).reshape(shp + (S // G,)),
+    stored = (mx - mn) * (np.float32(1) / np.float32(2 ** bits - 1))      # torch: tensor / scalar = tensor * (1/scalar)
+    return (w.reshape(shp + (S // fpi,)), stored.astype(x.dtype).reshape(shp + (S // G,)),
             mn.astype(x.dtype).reshape(shp + (S // G,)), q.reshape(x.shape))
 
 
