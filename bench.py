@@ -275,7 +275,7 @@ def main():
                        "l2_policy": "inputs larger than L2: every step streams the whole cache "
                                     f"({attn_bytes_all / max(1, n_attn) * L / 1e9:.1f} GB per step per GPU)",
                        "parallelism": f"batch-sharded x{world}, no data-path collective"},
-            "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "decode_attn_mma_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "peak_source": peak_src, "traffic": None,
                          "bytes_per_launch": attn_bytes_all / max(1, n_attn),

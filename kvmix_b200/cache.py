@@ -47,6 +47,7 @@ class KVmixLayerCache:
         self.k_group = 11 if k_bits == 3 else group_size       # modeling_llama_KVmix.py:49-52
         self.rk, self.rv, self.window = k_residual_ratio, v_residual_ratio, residual_length
         self.fk, self.fv = features_per_int(k_bits), features_per_int(v_bits)
+        max_tokens = _round_up(max_tokens, 32)                  # keeps every per-head base 16-byte aligned
         self.max_tokens = max_tokens
         dev = torch.device(device)
         B, H, D = batch, kv_heads, head_dim
@@ -173,6 +174,30 @@ class KVmixLayerCache:
                 self.vscale[:, :, :self.tvq].contiguous() if vq else None,
                 self.vmn[:, :, :self.tvq].contiguous() if vq else None,
                 self.kv_seq_len)
+
+    def load_tuple(self, past_key_value):
+        """Adopt an upstream 9-tuple (any of its tensors may be None): copies into the preallocated buffers."""
+        kq, kfull, ksc, kmn, vq, vfull, vsc, vmn, seen = past_key_value
+        self.reset()
+        if kq is not None:
+            self.tkq = kq.shape[3] * self.fk
+            self.kcode[..., :kq.shape[3]].copy_(kq)
+            self.kscale[..., :ksc.shape[3]].copy_(ksc)
+            self.kmn[..., :kmn.shape[3]].copy_(kmn)
+        if vq is not None:
+            self.tvq = vq.shape[2]
+            self.vcode[:, :, :self.tvq].copy_(vq)
+            self.vscale[:, :, :self.tvq].copy_(vsc)
+            self.vmn[:, :, :self.tvq].copy_(vmn)
+        self.k_len = 0 if kfull is None else kfull.shape[2]
+        self.v_len = 0 if vfull is None else vfull.shape[2]
+        if self.k_len > self.k_cap or self.v_len > self.v_cap:
+            raise RuntimeError("fp16 tail larger than the ring capacity (raise max_tail)")
+        if self.k_len:
+            self.kfull[:, :, :self.k_len].copy_(kfull)
+        if self.v_len:
+            self.vfull[:, :, :self.v_len].copy_(vfull)
+        self.kv_seq_len = int(seen)
 
     def packed_bytes(self):
         """Bytes one attend() must read: codes + scale/zero + fp16 tails (the roofline numerator)."""

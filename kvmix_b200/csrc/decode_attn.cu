@@ -26,12 +26,14 @@ struct SplitPlan {
 
 // Splits start on a packed-word and key-group boundary: multiples of 128 tokens, or of 352 = 11*32
 // for 3-bit keys (11 tokens per word).
-static SplitPlan plan_splits(int T, int k_bits, int64_t heads) {
-    const int unit = (k_bits == 3) ? 352 : 128;
+static SplitPlan plan_splits(int T, int k_bits, int64_t heads, bool mma_path = false) {
+    // the tensor-core kernel iterates 1024 tokens (352 for 3-bit keys) per CTA step and holds up to 8192 scores
+    const int unit = (k_bits == 3) ? 352 : (mma_path ? 1024 : 128);
+    const int kMaxChunk = mma_path ? ((k_bits == 3) ? 8096 : 8192) : kvq::kMaxChunk;
     const int64_t want_ctas = 148 * 4;
     int64_t n = (T + kMaxChunk - 1) / kMaxChunk;
     const int64_t by_fill = (want_ctas + heads - 1) / heads;
-    const int64_t by_len = (T + 4 * unit - 1) / (4 * unit);  // keep splits >= 4 units long
+    const int64_t by_len = mma_path ? (T + 2047) / 2048 : (T + 4 * unit - 1) / (4 * unit);  // keep splits long
     n = n > (by_fill < by_len ? by_fill : by_len) ? n : (by_fill < by_len ? by_fill : by_len);
     if (n < 1) n = 1;
     int chunk = (int)((T + n - 1) / n);
@@ -259,14 +261,23 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(kvq_attn_args
     }
 }
 
+// tensor-core path (decode_attn_mma.cu)
+bool mma_path_eligible(const kvq_attn_args &a);
+int launch_decode_attn_mma(const kvq_attn_args &a, int chunk, int n_splits, float *parts, unsigned int *counters,
+                           cudaStream_t st);
+
 }  // namespace kvq
 
 extern "C" uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32_t T) {
     using namespace kvq;
     if (B <= 0 || nh <= 0 || T <= 0) return 256;
     const int64_t heads = (int64_t)B * nh;
-    const SplitPlan p4 = plan_splits(T, 4, heads), p3 = plan_splits(T, 3, heads);
-    const int64_t ns = p4.n_splits > p3.n_splits ? p4.n_splits : p3.n_splits;
+    int64_t ns = 1;
+    for (int kb = 3; kb <= 4; ++kb)
+        for (int mma = 0; mma < 2; ++mma) {
+            const SplitPlan p = plan_splits(T, kb, heads, mma != 0);
+            if (p.n_splits > ns) ns = p.n_splits;
+        }
     uint64_t bytes = (uint64_t)heads * 4;
     bytes = (bytes + 255) / 256 * 256;
     bytes += (uint64_t)heads * ns * kPartStride * 4;
@@ -299,7 +310,8 @@ extern "C" int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream) {
         return KVQ_ERR_ALIGN;
 
     const int64_t heads = (int64_t)a->B * a->nh;
-    const SplitPlan plan = plan_splits(a->T, a->k_bits, heads);
+    const bool use_mma = mma_path_eligible(*a);
+    const SplitPlan plan = plan_splits(a->T, a->k_bits, heads, use_mma);
     if (heads * plan.n_splits > 2147483647LL) return KVQ_ERR_UNSUPPORTED;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     float *parts = nullptr;
@@ -313,6 +325,7 @@ extern "C" int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream) {
         int rc = record_cuda_error(cudaMemsetAsync(counters, 0, (size_t)heads * 4, st));
         if (rc) return rc;
     }
+    if (use_mma) return launch_decode_attn_mma(*a, plan.chunk, plan.n_splits, parts, counters, st);
     decode_attn_kernel<<<(unsigned)(heads * plan.n_splits), kAttnThreads, 0, st>>>(*a, plan.chunk, plan.n_splits,
                                                                                    parts, counters);
     return check_launch();

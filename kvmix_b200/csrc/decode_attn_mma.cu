@@ -1,0 +1,765 @@
+// Fused decode attention, tensor-core path (multi-head attention: one query head per kv head).
+//
+// Why tensor cores for a mat-vec: at the HBM rate a B200 has only ~1-3 issue slots per packed code
+// (2.8 per 2-bit code at 5.6 TB/s and 1.9 GHz).  Shift-mask-convert-FMA per code does not fit; one
+// logic op per *pair* of codes plus one mma.sync per 256 codes does.
+//
+// Codes go to the tensor core without ever being converted: a b-bit field left in place inside a
+// 16-bit lane, with all other bits masked off, *is* an fp16 subnormal with value field * 2^(pos-24).
+// mma.sync multiplies subnormal fp16 inputs exactly and accumulates in fp32, so the product with
+// the fp16 operand (q*scale, or p*scale) is exact and the power of two is undone per output row in
+// the epilogue.  Pairs along the contraction axis are formed with one byte-permute of two words.
+//
+// Keys (codes [D, T/fpi], one word = fpi tokens of one channel; scale/zero [D, T/G]):
+//   A (16x16) = codes, rows = tokens, cols = 16 channels;  B (16x8) = q[d] * scale[d, group n]
+//   for the 8 token groups of the warp tile (one column per group of the lane-octet that owns the
+//   row), so one B fragment serves 256 tokens; the zero term  sum_d q[d]*zero[d,g]  is accumulated
+//   in fp32 on the CUDA cores once per group.  Code words and scale/zero tiles stream through a
+//   per-warp multi-stage cp.async ring in shared memory (128-bit copies, several KB in flight per warp).
+// Values (codes [T, D/fpi], one word = fpi channels of one token; scale/zero [T, D/G]):
+//   A (16x16) = codes, rows = channels, cols = 16 tokens;  B (16x8): column 2j = p[t]*scale[t,j],
+//   column 2j+1 = p[t]*zero[t,j]; one extra MMA with A = ones sums the zero columns.
+// The fp16 tails and the softmax run on the CUDA cores as in the generic kernel.
+#include "common.cuh"
+
+namespace kvq {
+
+constexpr int kMmaThreads = 128;
+constexpr int kMmaWarps = 4;
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// ---------------------------------------------------------------------------------------------
+// Field extraction.  unpack(wa, wb, r): r[i] = fp16x2 { field i of wa (low), field i of wb (high) }
+// left at bit position pos(i) inside each 16-bit half, i.e. the subnormal pair
+// { f_a * 2^(pos-24), f_b * 2^(pos-24) }.  inv_scale(i) = 2^(24-pos(i)).
+template <int BITS> struct Fields;
+
+template <> struct Fields<4> {
+    static constexpr int N = 8;
+    __device__ static __forceinline__ int pos(int i) { return (i & 1) ? 4 : 0; }
+    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[8]) {
+        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
+        const uint32_t los = lo >> 8, his = hi >> 8;
+        r[0] = lo & 0x000f000fu; r[1] = lo & 0x00f000f0u; r[2] = los & 0x000f000fu; r[3] = los & 0x00f000f0u;
+        r[4] = hi & 0x000f000fu; r[5] = hi & 0x00f000f0u; r[6] = his & 0x000f000fu; r[7] = his & 0x00f000f0u;
+    }
+};
+
+template <> struct Fields<2> {
+    static constexpr int N = 16;
+    __device__ static __forceinline__ int pos(int i) { const int t = i & 7; return t < 5 ? 2 * t : 2 * (t - 5); }
+    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[16]) {
+        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
+        const uint32_t los = lo >> 10, his = hi >> 10;
+#pragma unroll
+        for (int t = 0; t < 5; ++t) { r[t] = lo & (0x00030003u << (2 * t)); r[8 + t] = hi & (0x00030003u << (2 * t)); }
+#pragma unroll
+        for (int t = 5; t < 8; ++t) {
+            r[t] = los & (0x00030003u << (2 * (t - 5)));
+            r[8 + t] = his & (0x00030003u << (2 * (t - 5)));
+        }
+    }
+};
+
+template <> struct Fields<1> {
+    static constexpr int N = 32;
+    __device__ static __forceinline__ int pos(int i) { const int t = i & 15; return t < 10 ? t : t - 10; }
+    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[32]) {
+        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
+        const uint32_t los = lo >> 10, his = hi >> 10;
+#pragma unroll
+        for (int t = 0; t < 10; ++t) { r[t] = lo & (0x00010001u << t); r[16 + t] = hi & (0x00010001u << t); }
+#pragma unroll
+        for (int t = 10; t < 16; ++t) { r[t] = los & (0x00010001u << (t - 10)); r[16 + t] = his & (0x00010001u << (t - 10)); }
+    }
+};
+
+// 3-bit words: fields 0..9 at bits 3i, field 10 (2 bits) at bit 30.
+template <> struct Fields<3> {
+    static constexpr int N = 11;
+    __device__ static __forceinline__ int pos(int i) {
+        constexpr int P[11] = {0, 3, 6, 0, 3, 0, 3, 6, 0, 3, 0};
+        return P[i];
+    }
+    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[11]) {
+        const uint32_t x0 = prmt(wa, wb, 0x5410), x1 = x0 >> 9;
+        const uint32_t y = prmt(wa >> 15, wb >> 15, 0x5410), y1 = y >> 9;
+        const uint32_t z1 = prmt(wa, wb, 0x7632) >> 14;
+        r[0] = x0 & 0x00070007u; r[1] = x0 & 0x00380038u; r[2] = x0 & 0x01c001c0u;
+        r[3] = x1 & 0x00070007u; r[4] = x1 & 0x00380038u;
+        r[5] = y & 0x00070007u; r[6] = y & 0x00380038u; r[7] = y & 0x01c001c0u;
+        r[8] = y1 & 0x00070007u; r[9] = y1 & 0x00380038u;
+        r[10] = z1 & 0x00030003u;
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Key-side geometry per bit width.  A warp tile is 8 lane-octets x TPO tokens; code words reach the
+// warp through its own ring of cp.async stages in shared memory (padded rows so the fragment loads
+// are bank-conflict free), three stages in flight ahead of the math.  All shared-memory offsets are
+// compile-time constants relative to one per-lane base; global addresses advance by per-stage strides.
+template <int KB> struct KGeom {
+    static constexpr int FPI = fields_per_word(KB);
+    static constexpr int WPL = (KB == 4) ? 4 : (KB == 2) ? 2 : 1;     // words per octet: 32 tokens (11 for 3-bit)
+    static constexpr int TPO = WPL * FPI;                              // tokens per octet chunk
+    static constexpr int WT = 8 * TPO;                                 // tokens per warp tile (256 / 88)
+    static constexpr int KSPS = (KB == 4) ? 1 : 2;                     // k-steps (16 channels) per stage
+    static constexpr int NSTAGE = 8 / KSPS;                            // stages per warp tile: 8 / 4
+    static constexpr int NMMA = (TPO + 1) / 2;                         // MMAs (token pairs) per octet chunk
+    static constexpr int RB = 32 * WPL;                                // code bytes per channel row per warp tile
+    static constexpr int RS = RB + 16;                                 // padded row stride in the ring
+    static constexpr int ROWS = 16 * KSPS;                             // channel rows per stage
+    static constexpr int STAGE_BYTES = ROWS * RS;                      // 2304 / 2560 / 1536
+    static constexpr int GPR = RB / 16;                                // 16-byte granules per row: 8 / 4 / 2
+    static constexpr int GPL = ROWS * GPR / 32;                        // granules per lane per stage: 4 / 4 / 2
+    static constexpr int RPI = 32 / GPR;                               // rows between a lane's granules
+    static constexpr int NS = 4;                                       // ring slots (NSTAGE % NS == 0: slots are static)
+    static constexpr int P = NS - 1;                                   // stages in flight
+    static constexpr int SZ_BYTES = 2 * kHeadDim * 16;                 // scale + zero tile: 16 B per channel row
+    static constexpr int WARP_BYTES = NS * STAGE_BYTES + SZ_BYTES;
+    static constexpr float MID = (float)((1 << KB) - 1) * 0.5f;        // codes are centred on the group midpoint
+};
+
+template <int WPL> struct WordVec;
+template <> struct WordVec<1> { using T = uint32_t; };
+template <> struct WordVec<2> { using T = uint2; };
+template <> struct WordVec<4> { using T = uint4; };
+
+template <int VB> struct VGeom {
+    static constexpr int FPI = fields_per_word(VB);
+    static constexpr int RBV = kHeadDim / FPI * 4;                     // code bytes per token row: 64 / 32 / 16
+    static constexpr int TPS = 32;                                     // tokens per stage (2 k-steps)
+    static constexpr int GPT = RBV / 16;                               // granules per token row: 4 / 2 / 1
+    static constexpr int GPL = (TPS * GPT + 31) / 32;                  // code granules per lane per stage: 4 / 2 / 1
+    static constexpr int SZ_OFF = TPS * RBV;                           // scale rows, then zero rows (<= 4 groups each)
+    static constexpr int STAGE_BYTES = TPS * RBV + 2 * TPS * 4 * 2;
+    static constexpr int NS = (VB == 4) ? 4 : (VB == 2) ? 6 : 8;
+    static constexpr int P = NS - 1;
+    static constexpr int PB_OFF = NS * STAGE_BYTES;                    // operand tile p*scale / p*mid: 16 token pairs x 8 cols
+    static constexpr int WARP_BYTES = NS * STAGE_BYTES + 16 * 8 * 4;
+    static constexpr float MID = (float)((1 << VB) - 1) * 0.5f;
+};
+
+template <int KB, int VB> constexpr int warp_region_bytes() {
+    return KGeom<KB>::WARP_BYTES > VGeom<VB>::WARP_BYTES ? KGeom<KB>::WARP_BYTES : VGeom<VB>::WARP_BYTES;
+}
+
+template <int BYTES>
+__device__ __forceinline__ void cp_async(uint32_t smem_addr, const void *gmem) {
+    if constexpr (BYTES == 16) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem));
+    } else {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(smem_addr), "l"(gmem), "n"(BYTES));
+    }
+}
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+
+struct MmaSmem {
+    float *scores;          // [n_scores]
+    unsigned char *ring;    // this warp's region
+    float *tailred;         // [kMmaWarps][kHeadDim] partial sums of the fp16 value tail
+    __half *q;              // [kHeadDim]
+    float *misc;            // [16]
+};
+
+// ---------------------------------------------------------------------------------------------
+// q . K^T over packed keys for tokens [t0, hi) (t0 is a multiple of 1024, or 352 for 3-bit keys).
+// Scores (already multiplied by softmax_scale) go to sm.scores[t - t0].  Warps work independently:
+// warp w takes warp tiles w, w+4, ... and streams their code words through its own ring.
+template <int KB>
+__device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int32_t *kc, const __half *ks,
+                                              const __half *kz, const MmaSmem &sm, int t0, int hi) {
+    using G = KGeom<KB>;
+    using F = Fields<KB>;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+    const int Gk = a.k_group;
+    const int n_words = a.Tkq / G::FPI;                       // valid code words per channel row
+    const int n_tiles = (hi - t0 + G::WT - 1) / G::WT;
+    const int my_tiles = (n_tiles - warp + kMmaWarps - 1) / kMmaWarps;   // tiles warp, warp+4, ...
+    if (my_tiles <= 0) return;
+
+    const int kc_sD = (int)a.kc_sD, ks_sD = (int)a.ks_sD;
+    // ---- per-lane constants --------------------------------------------------------------------
+    const uint32_t ring_s = smem_u32(sm.ring);
+    const uint32_t sz_s = ring_s + G::NS * G::STAGE_BYTES;                    // [2][128][8] halfs
+    const int gr = lane % G::GPR, row0 = lane / G::GPR;
+    const uint32_t cp_dst = ring_s + row0 * G::RS + gr * 16;                   // + slot*STAGE + i*RPI*RS
+    const uint32_t frag_s = ring_s + (2 * tig) * G::RS + g * (4 * G::WPL);     // + slot*STAGE + (16k + rr)*RS
+    const int gw = (g * G::TPO) / Gk;                                          // group of this octet inside the warp tile
+    const uint32_t szl_s = sz_s + ((2 * tig) * 8 + gw) * 2;                    // + (16 ksx + {0,1,8,9}) * 16 [+ 2048 for zero]
+    const uint32_t q_s = smem_u32(sm.q) + (2 * tig) * 2;                       // + 32 ksx [+16]
+    const int ngw = (G::WT + Gk - 1) / Gk;                                     // groups per warp tile: 8 / 4 / 2
+    const uint32_t szcp_dst = sz_s + lane * 16;                                // + i*512
+    const int tile_words = kMmaWarps * G::WT / G::FPI;                         // word-column distance between my tiles
+    const int tile_groups = kMmaWarps * G::WT / Gk;
+
+    const int32_t *tb_cur = kc + (int64_t)row0 * kc_sD + (t0 + warp * G::WT) / G::FPI + 4 * gr;
+    const __half *ks_cur = ks + (int64_t)lane * ks_sD + (t0 + warp * G::WT) / Gk;
+    const __half *kz_cur = kz + (int64_t)lane * ks_sD + (t0 + warp * G::WT) / Gk;
+    int wcol_cur = (t0 + warp * G::WT) / G::FPI + 4 * gr;                      // this lane's granule word column
+    bool ok_cur = wcol_cur < n_words;
+
+    auto issue_stage = [&](const int32_t *tb, bool ok, int sst) {              // sst: compile-time stage of the tile
+        if (ok) {
+            const uint32_t dst = cp_dst + (sst % G::NS) * G::STAGE_BYTES;
+#pragma unroll
+            for (int i = 0; i < G::GPL; ++i)
+                cp_async<16>(dst + i * G::RPI * G::RS, tb + (sst * G::ROWS + i * G::RPI) * kc_sD);
+        }
+    };
+    auto issue_sz = [&](const __half *ps, const __half *pz) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int off = 32 * i * ks_sD;
+            if (ngw == 8) { cp_async<16>(szcp_dst + i * 512, ps + off); cp_async<16>(szcp_dst + 2048 + i * 512, pz + off); }
+            else if (ngw == 4) { cp_async<8>(szcp_dst + i * 512, ps + off); cp_async<8>(szcp_dst + 2048 + i * 512, pz + off); }
+            else { cp_async<4>(szcp_dst + i * 512, ps + off); cp_async<4>(szcp_dst + 2048 + i * 512, pz + off); }
+        }
+    };
+
+    issue_sz(ks_cur, kz_cur);
+    issue_stage(tb_cur, ok_cur, 0);
+    cp_async_commit();
+    issue_stage(tb_cur, ok_cur, 1);
+    cp_async_commit();
+    issue_stage(tb_cur, ok_cur, 2);
+    cp_async_commit();
+
+    const uint32_t ones = 0x3c003c00u;
+    for (int j = 0; j < my_tiles; ++j) {
+        const int tile0 = t0 + (j * kMmaWarps + warp) * G::WT;
+        const int tok0 = tile0 + g * G::TPO;                   // first token of this octet's chunk
+        const bool live = tok0 < hi;                           // chunks are whole or absent (hi is a group multiple)
+        const bool have_next = j + 1 < my_tiles;
+        const int32_t *tb_nxt = tb_cur + tile_words;
+        const bool ok_nxt = have_next && (wcol_cur + tile_words < n_words);
+
+        // the scale/zero tile of this warp tile was committed at least 3 groups ago
+        cp_async_wait<2>();
+        __syncwarp();
+        // ---- B fragments q*scale and the zero term sum_d q[d]*zero[d,g] ----------------------------------
+        // q*scale needs 22 bits; it is carried as an fp16 pair hi + lo (lo = fma(q, s, -hi) is exact) and every
+        // code tile is multiplied by both, so the key side adds no rounding beyond the fp32 accumulation.  The
+        // zero term gets the same treatment and is summed over channels by an MMA whose A operand is all ones.
+        uint32_t bq[8][2], bl[8][2];
+        float accz[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ksx = 0; ksx < 8; ++ksx) {
+            const __half2 q01 = as_h2(lds32(q_s + 32 * ksx)), q89 = as_h2(lds32(q_s + 32 * ksx + 16));
+            const uint32_t so = szl_s + ksx * 256;
+            const __half2 s01 = as_h2(lds16(so) | (lds16(so + 16) << 16)), s89 = as_h2(lds16(so + 128) | (lds16(so + 144) << 16));
+            const __half2 z01 = as_h2(lds16(so + 2048) | (lds16(so + 2064) << 16));
+            const __half2 z89 = as_h2(lds16(so + 2176) | (lds16(so + 2192) << 16));
+            const __half2 b01 = __hmul2(q01, s01), b89 = __hmul2(q89, s89);
+            const __half2 y01 = __hmul2(q01, z01), y89 = __hmul2(q89, z89);
+            bq[ksx][0] = as_u32(b01);
+            bq[ksx][1] = as_u32(b89);
+            bl[ksx][0] = as_u32(__hfma2(q01, s01, __hneg2(b01)));
+            bl[ksx][1] = as_u32(__hfma2(q89, s89, __hneg2(b89)));
+            mma16816(accz, ones, ones, ones, ones, as_u32(y01), as_u32(y89));
+            mma16816(accz, ones, ones, ones, ones, as_u32(__hfma2(q01, z01, __hneg2(y01))), as_u32(__hfma2(q89, z89, __hneg2(y89))));
+        }
+        __syncwarp();                                          // everyone has read the tile: it may be refilled
+
+        float acc[G::NMMA][4];
+#pragma unroll
+        for (int m = 0; m < G::NMMA; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+
+#pragma unroll
+        for (int st = 0; st < G::NSTAGE; ++st) {
+            // issue stage st+P (of this tile or the next); the next tile's scale/zero tile rides with its first stage
+            if (st + G::P < G::NSTAGE) {
+                issue_stage(tb_cur, ok_cur, st + G::P);
+            } else {
+                issue_stage(tb_nxt, ok_nxt, st + G::P - G::NSTAGE);
+            }
+            if (st == 0 && have_next) issue_sz(ks_cur + tile_groups, kz_cur + tile_groups);
+            cp_async_commit();
+            cp_async_wait<G::P>();
+            __syncwarp();
+            const uint32_t src = frag_s + (st % G::NS) * G::STAGE_BYTES;
+#pragma unroll
+            for (int k = 0; k < G::KSPS; ++k) {
+                const int ksx = st * G::KSPS + k;
+                uint32_t w[4][G::WPL];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const uint32_t ad = src + (k * 16 + (r & 1) + (r >> 1) * 8) * G::RS;
+                    if constexpr (G::WPL == 4) {
+                        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+                                     : "=r"(w[r][0]), "=r"(w[r][1]), "=r"(w[r][2]), "=r"(w[r][3]) : "r"(ad));
+                    } else if constexpr (G::WPL == 2) {
+                        asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];\n" : "=r"(w[r][0]), "=r"(w[r][1]) : "r"(ad));
+                    } else {
+                        w[r][0] = lds32(ad);
+                    }
+                }
+#pragma unroll
+                for (int x = 0; x < G::WPL; ++x) {
+                    uint32_t rlo[F::N], rhi[F::N];
+                    F::unpack(w[0][x], w[1][x], rlo);
+                    F::unpack(w[2][x], w[3][x], rhi);
+#pragma unroll
+                    for (int i = 0; i < F::N; i += 2) {
+                        const int m = (x * F::N + i) / 2;
+                        const uint32_t a1 = (i + 1 < F::N) ? rlo[i + 1] : 0u, a3 = (i + 1 < F::N) ? rhi[i + 1] : 0u;
+                        mma16816(acc[m], rlo[i], a1, rhi[i], a3, bq[ksx][0], bq[ksx][1]);
+                        mma16816(acc[m], rlo[i], a1, rhi[i], a3, bl[ksx][0], bl[ksx][1]);
+                    }
+                }
+            }
+            __syncwarp();                                      // slot st % NS is free for the stage NS ahead
+        }
+
+        // ---- epilogue: the octet's column is n = g, held by the lane with tig == g/2 -----------------
+        if (live && tig == (g >> 1)) {
+            const bool sel = g & 1;
+            const float corr = sel ? accz[1] : accz[0];
+            float *dst = sm.scores + (tok0 - t0);
+#pragma unroll
+            for (int m = 0; m < G::NMMA; ++m) {
+                const int i0 = 2 * m, i1 = 2 * m + 1;
+                float s0 = fmaf(sel ? acc[m][1] : acc[m][0], (float)(1 << (24 - F::pos(i0 % F::N))), corr);
+                float s1 = (i1 < G::TPO) ? fmaf(sel ? acc[m][3] : acc[m][2], (float)(1 << (24 - F::pos(i1 % F::N))), corr) : 0.f;
+                if (a.round_scores) {
+                    const float2 r = __half22float2(__floats2half2_rn(s0, s1));
+                    s0 = r.x;
+                    s1 = r.y;
+                }
+                if (i1 < G::TPO && (G::TPO % 2 == 0)) {
+                    *reinterpret_cast<float2 *>(dst + i0) = make_float2(s0 * a.softmax_scale, s1 * a.softmax_scale);
+                } else {
+                    dst[i0] = s0 * a.softmax_scale;
+                    if (i1 < G::TPO) dst[i1] = s1 * a.softmax_scale;
+                }
+            }
+        }
+        tb_cur = tb_nxt;
+        ok_cur = ok_nxt;
+        wcol_cur += tile_words;
+        ks_cur += tile_groups;
+        kz_cur += tile_groups;
+    }
+    cp_async_wait<0>();
+}
+
+// ---------------------------------------------------------------------------------------------
+// p . V over packed values for tokens [t0, hi), (hi - t0) % 32 == 0.  sm.scores holds p.  Warp w
+// takes 32-token blocks w, w+4, ... through its own ring (codes + scale + zero rows per stage).  Per
+// stage the warp first forms the B operands once for all its lanes (p*scale and p*midpoint for 16
+// token pairs x 8 columns, half2 per pair) in a small tile, then every lane reads its two B registers
+// per k-step with one 32-bit load each.  Returns this warp's 128 partial channel sums in its own
+// ring region (float [128] at the region base).
+template <int VB>
+__device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int32_t *vc, const __half *vs,
+                                              const __half *vz, const MmaSmem &sm, int t0, int hi) {
+    using G = VGeom<VB>;
+    using F = Fields<VB>;
+    constexpr int WPO = (VB == 4) ? 2 : 1;                    // words per octet (16 channels)
+    constexpr int NF = (VB == 1) ? 16 : F::N;                 // fields used per word (1-bit: one 16-bit half)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+    const int Gv = a.v_group;
+    const int ngv = kHeadDim / Gv;                            // channel groups: 4 / 2 / 1
+    const int grp = (16 * g) / Gv;                            // channel group of this octet
+    const int n_blocks = (hi - t0 + G::TPS - 1) / G::TPS;
+    const int my_blocks = (n_blocks - warp + kMmaWarps - 1) / kMmaWarps;
+    float *my_red = reinterpret_cast<float *>(sm.ring);
+    if (my_blocks <= 0) {
+        for (int i = lane; i < kHeadDim; i += 32) my_red[i] = 0.f;
+        return;
+    }
+
+    // ---- per-lane constants ----------------------------------------------------------------------
+    const uint32_t ring_s = smem_u32(sm.ring);
+    const uint32_t pb_s = ring_s + G::PB_OFF;
+    // cp.async: granule x = lane + 32 i -> token row tl = x / GPT, granule gr = x % GPT (source is contiguous)
+    const int cp_tl0 = lane / G::GPT, cp_gr = lane % G::GPT;
+    const int cp_grs = (VB == 4) ? (cp_gr ^ (2 * ((cp_tl0 >> 1) & 1))) : cp_gr;          // bank swizzle (4-bit rows)
+    const uint32_t cp_dst = ring_s + cp_tl0 * G::RBV + cp_grs * 16;                      // + slot*STAGE + i*(32/GPT)*RBV
+    // fragment loads: token tl = 16 h2 + tig + 4 i
+    uint32_t frag_s;
+    if (VB == 4) frag_s = ring_s + tig * G::RBV + (((g >> 1) ^ (2 * ((tig >> 1) & 1))) * 16) + (g & 1) * 8;   // swizzled granule
+    else if (VB == 2) frag_s = ring_s + tig * G::RBV + 4 * g;
+    else frag_s = ring_s + tig * G::RBV + 4 * (g >> 1);
+    const int wshift = (VB == 1) ? 16 * (g & 1) : 0;
+    // operand tile: pair pi = 8 h2 + 4 b + tig holds tokens (16 h2 + 8 b + tig, +4); reader column g
+    const uint32_t pb_rd = pb_s + (tig * 8 + g) * 4;                                     // + (8 h2 + 4 b) * 32
+    // operand build: lane -> pair pi = lane & 15, column half ch = lane >> 4 (groups 2ch, 2ch+1)
+    const int pi = lane & 15, ch = lane >> 4;
+    const int bt0 = 16 * (pi >> 3) + 8 * ((pi >> 2) & 1) + (pi & 3), bt1 = bt0 + 4;      // the pair's tokens in the stage
+    const int g0 = min(2 * ch, ngv - 1), g1 = min(2 * ch + 1, ngv - 1);                  // clamped: dead columns are zeroed below
+    const float live0 = (2 * ch < ngv) ? 1.f : 0.f, live1 = (2 * ch + 1 < ngv) ? 1.f : 0.f;
+    const uint32_t o00 = ring_s + G::SZ_OFF + (bt0 * ngv + g0) * 2, o01 = ring_s + G::SZ_OFF + (bt0 * ngv + g1) * 2;
+    const uint32_t o10 = ring_s + G::SZ_OFF + (bt1 * ngv + g0) * 2, o11 = ring_s + G::SZ_OFF + (bt1 * ngv + g1) * 2;
+    const uint32_t pb_wr = pb_s + (pi * 8 + 4 * ch) * 4;
+
+    const int block_stride = kMmaWarps * G::TPS;
+    const char *src_codes = reinterpret_cast<const char *>(vc + (int64_t)(t0 + warp * G::TPS) * a.vc_sT) + lane * 16;
+    const int ngran = 4 * ngv;                                                           // 16-byte granules per array per stage
+    const int sz_arr = lane >= ngran ? 1 : 0;                                            // 0: scale rows, 1: zero rows
+    const int sz_off = (lane - sz_arr * ngran) * 16;
+    const bool sz_on = lane < 2 * ngran;
+    const char *src_sz = reinterpret_cast<const char *>((sz_arr ? vz : vs) + (int64_t)(t0 + warp * G::TPS) * a.vs_sT) + sz_off;
+    const uint32_t sz_dst = ring_s + G::SZ_OFF + sz_arr * (G::TPS * 4 * 2) + sz_off;
+    const int64_t codes_step = (int64_t)block_stride * G::RBV, sz_step = (int64_t)block_stride * ngv * 2;
+
+    int to_issue = my_blocks;                                                            // blocks not yet issued
+    auto issue_stage = [&](uint32_t slot_off) {
+        if (to_issue > 0) {
+#pragma unroll
+            for (int i = 0; i < G::GPL; ++i)
+                if (G::TPS * G::GPT % 32 == 0 || lane + 32 * i < G::TPS * G::GPT)
+                    cp_async<16>(cp_dst + slot_off + i * (32 / G::GPT) * G::RBV, src_codes + i * 512);
+            if (sz_on) cp_async<16>(sz_dst + slot_off, src_sz);
+        }
+        --to_issue;
+        src_codes += codes_step;
+        src_sz += sz_step;
+    };
+
+    float acc[8][4], accz[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+    const uint32_t ones = 0x3c003c00u;
+
+#pragma unroll
+    for (int q = 0; q < G::P; ++q) { issue_stage(q * G::STAGE_BYTES); cp_async_commit(); }
+
+    uint32_t st = 0, issue_st = G::P * G::STAGE_BYTES;         // byte offsets of the slot being read / filled
+    const float *pp = sm.scores + warp * G::TPS;               // p of this warp's current block
+    for (int q = 0; q < my_blocks; ++q) {
+        issue_stage(issue_st);
+        cp_async_commit();
+        cp_async_wait<G::P>();
+        __syncwarp();
+        // ---- B operands for the stage: 16 token pairs x 8 columns -----------------------------------
+        {
+            const float p0 = pp[bt0], p1 = pp[bt1];
+            const float s00 = live0 * __half2float(__ushort_as_half((unsigned short)lds16(o00 + st)));
+            const float s01 = live1 * __half2float(__ushort_as_half((unsigned short)lds16(o01 + st)));
+            const float s10 = live0 * __half2float(__ushort_as_half((unsigned short)lds16(o10 + st)));
+            const float s11 = live1 * __half2float(__ushort_as_half((unsigned short)lds16(o11 + st)));
+            const float z00 = live0 * __half2float(__ushort_as_half((unsigned short)lds16(o00 + st + 256)));
+            const float z01 = live1 * __half2float(__ushort_as_half((unsigned short)lds16(o01 + st + 256)));
+            const float z10 = live0 * __half2float(__ushort_as_half((unsigned short)lds16(o10 + st + 256)));
+            const float z11 = live1 * __half2float(__ushort_as_half((unsigned short)lds16(o11 + st + 256)));
+            // columns 4ch .. 4ch+3 = (p*scale_g0, p*mid_g0, p*scale_g1, p*mid_g1), each a half2 over the token pair;
+            // mid = zero + MID*scale is the midpoint of the group: codes are used as (code - MID)
+            const uint32_t c0 = as_u32(__floats2half2_rn(p0 * s00, p1 * s10));
+            const uint32_t c1 = as_u32(__floats2half2_rn(p0 * fmaf(G::MID, s00, z00), p1 * fmaf(G::MID, s10, z10)));
+            const uint32_t c2 = as_u32(__floats2half2_rn(p0 * s01, p1 * s11));
+            const uint32_t c3 = as_u32(__floats2half2_rn(p0 * fmaf(G::MID, s01, z01), p1 * fmaf(G::MID, s11, z11)));
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(pb_wr), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+        }
+        __syncwarp();
+        const uint32_t fs = frag_s + st;
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            const uint32_t b0 = lds32(pb_rd + (8 * h2) * 32), b1 = lds32(pb_rd + (8 * h2 + 4) * 32);
+            uint32_t w[4][WPO];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t ad = fs + (16 * h2 + 4 * i) * G::RBV;          // token 16 h2 + 4 i + tig (tig is in frag_s)
+                if constexpr (VB == 4) {
+                    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];\n" : "=r"(w[i][0]), "=r"(w[i][WPO - 1]) : "r"(ad));
+                } else {
+                    w[i][0] = lds32(ad) >> wshift;
+                }
+            }
+            mma16816(accz, ones, ones, ones, ones, b0, b1);
+#pragma unroll
+            for (int x = 0; x < WPO; ++x) {
+                uint32_t rlo[F::N], rhi[F::N];
+                F::unpack(w[0][x], w[1][x], rlo);              // tokens (tig, tig+4)    -> k cols 2tig, 2tig+1
+                F::unpack(w[2][x], w[3][x], rhi);              // tokens (tig+8, tig+12) -> k cols 2tig+8, 2tig+9
+#pragma unroll
+                for (int i = 0; i < NF; i += 2) {
+                    const int m = (x * NF + i) / 2;
+                    mma16816(acc[m], rlo[i], rlo[i + 1], rhi[i], rhi[i + 1], b0, b1);
+                }
+            }
+        }
+        __syncwarp();
+        st = (st + G::STAGE_BYTES == G::NS * G::STAGE_BYTES) ? 0u : st + G::STAGE_BYTES;
+        issue_st = (issue_st + G::STAGE_BYTES == G::NS * G::STAGE_BYTES) ? 0u : issue_st + G::STAGE_BYTES;
+        pp += block_stride;
+    }
+    cp_async_wait<0>();
+    __syncwarp();
+    // epilogue: channel c = 16 g + i (i = 2m + r); columns 2*grp (sum p*scale) and 2*grp+1 (sum p*mid) sit in tig == grp
+    if (tig == grp) {
+        float *red = my_red + 16 * g;
+        const float corr = accz[1] - G::MID * accz[0];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int i = 2 * m + r;
+                const int fi = i % NF;
+                red[i] = fmaf(acc[m][2 * r], (float)(1 << (24 - F::pos(fi))), corr);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// q . K^T over the fp16 tail for tokens [lo, t1): 16-token tiles on the tensor core, straight from
+// global memory (row g and g+8 of a tile per lane-octet, 16-byte loads of 8 channels; the k axis is
+// permuted identically in the q fragments).  Every B column carries q, so each lane sees its rows' sums.
+__device__ __forceinline__ void qk_tail_mma(const kvq_attn_args &a, const __half *kf, const MmaSmem &sm, int t0,
+                                            int lo, int t1) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+    uint4 qf[4];
+#pragma unroll
+    for (int S = 0; S < 4; ++S) qf[S] = *reinterpret_cast<const uint4 *>(sm.q + 32 * S + 8 * tig);
+    const int n_tiles = (t1 - lo + 15) / 16;
+    for (int tile = warp; tile < n_tiles; tile += kMmaWarps) {
+        const int ta = lo + 16 * tile + g, tb = ta + 8;
+        int sa = a.kf_start + (min(ta, t1 - 1) - a.Tkq), sb = a.kf_start + (min(tb, t1 - 1) - a.Tkq);
+        if (sa >= a.kf_cap) sa -= a.kf_cap;
+        if (sb >= a.kf_cap) sb -= a.kf_cap;
+        const __half *pa = kf + (int64_t)sa * a.kf_sT + 8 * tig, *pb = kf + (int64_t)sb * a.kf_sT + 8 * tig;
+        uint4 ra[4], rb[4];
+#pragma unroll
+        for (int S = 0; S < 4; ++S) {
+            ra[S] = __ldg(reinterpret_cast<const uint4 *>(pa + 32 * S));
+            rb[S] = __ldg(reinterpret_cast<const uint4 *>(pb + 32 * S));
+        }
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int S = 0; S < 4; ++S) {
+            mma16816(c, ra[S].x, rb[S].x, ra[S].y, rb[S].y, qf[S].x, qf[S].y);
+            mma16816(c, ra[S].z, rb[S].z, ra[S].w, rb[S].w, qf[S].z, qf[S].w);
+        }
+        if (tig == 0) {
+            float s0 = c[0], s1 = c[2];
+            if (a.round_scores) {
+                const float2 r = __half22float2(__floats2half2_rn(s0, s1));
+                s0 = r.x;
+                s1 = r.y;
+            }
+            if (ta < t1) sm.scores[ta - t0] = s0 * a.softmax_scale;
+            if (tb < t1) sm.scores[tb - t0] = s1 * a.softmax_scale;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+template <int KB, int VB>
+__global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_attn_args a, int chunk, int n_splits,
+                                                                     int n_scores, float *__restrict__ parts,
+                                                                     unsigned int *__restrict__ counters) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    MmaSmem sm;
+    sm.scores = reinterpret_cast<float *>(smem_raw);
+    unsigned char *after_scores = smem_raw + (size_t)n_scores * 4;
+    sm.ring = after_scores + warp * warp_region_bytes<KB, VB>();
+    sm.tailred = reinterpret_cast<float *>(after_scores + kMmaWarps * warp_region_bytes<KB, VB>());
+    sm.q = reinterpret_cast<__half *>(sm.tailred + kMmaWarps * kHeadDim);
+    sm.misc = reinterpret_cast<float *>(sm.q + kHeadDim);
+
+    const int split = blockIdx.x % n_splits;
+    const int s = blockIdx.x / n_splits;                      // b * nh + h  (nh == nh_kv on this path)
+    const int b = s / a.nh, h = s % a.nh;
+    const int t0 = split * chunk, t1 = min(a.T, t0 + chunk);
+
+    const __half *q = static_cast<const __half *>(a.q) + (int64_t)b * a.q_sB + (int64_t)h * a.q_sH;
+    if (tid < kHeadDim) sm.q[tid] = q[tid];
+    for (int i = tid; i < kMmaWarps * kHeadDim; i += kMmaThreads) sm.tailred[i] = 0.f;
+    __syncthreads();
+
+    // ---- 1. scores ------------------------------------------------------------------------------
+    {
+        const int hi = min(t1, a.Tkq);
+        if (t0 < hi) {
+            const int32_t *kc = a.kcode + (int64_t)b * a.kc_sB + (int64_t)h * a.kc_sH;
+            const __half *ks = static_cast<const __half *>(a.kscale) + (int64_t)b * a.ks_sB + (int64_t)h * a.ks_sH;
+            const __half *kz = static_cast<const __half *>(a.kmn) + (int64_t)b * a.ks_sB + (int64_t)h * a.ks_sH;
+            qk_packed_mma<KB>(a, kc, ks, kz, sm, t0, hi);
+        }
+        const int lo = max(t0, a.Tkq);
+        if (lo < t1) {
+            const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)h * a.kf_sH;
+            qk_tail_mma(a, kf, sm, t0, lo, t1);
+        }
+    }
+    __syncthreads();
+
+    // ---- 2. softmax numerators ------------------------------------------------------------------
+    const int n = t1 - t0;
+    float m = -3.0e38f;
+    for (int i = tid; i < n; i += kMmaThreads) m = fmaxf(m, sm.scores[i]);
+    m = warp_max(m);
+    if (lane == 0) sm.misc[warp] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(sm.misc[0], sm.misc[1]), fmaxf(sm.misc[2], sm.misc[3]));
+    float l = 0.f;
+    for (int i = tid; i < n; i += kMmaThreads) {
+        const float p = __expf(sm.scores[i] - m);
+        sm.scores[i] = p;
+        l += p;
+    }
+    l = warp_sum(l);
+    if (lane == 0) sm.misc[4 + warp] = l;
+    __syncthreads();
+    l = (sm.misc[4] + sm.misc[5]) + (sm.misc[6] + sm.misc[7]);
+
+    // ---- 3. p.V -----------------------------------------------------------------------------------
+    {
+        const int hi = min(t1, a.Tvq);
+        if (t0 < hi) {
+            const int32_t *vc = a.vcode + (int64_t)b * a.vc_sB + (int64_t)h * a.vc_sH;
+            const __half *vs = static_cast<const __half *>(a.vscale) + (int64_t)b * a.vs_sB + (int64_t)h * a.vs_sH;
+            const __half *vz = static_cast<const __half *>(a.vmn) + (int64_t)b * a.vs_sB + (int64_t)h * a.vs_sH;
+            pv_packed_mma<VB>(a, vc, vs, vz, sm, t0, hi);
+        }
+        const int lo = max(t0, a.Tvq);
+        if (lo < t1) {
+            const __half *vf = static_cast<const __half *>(a.vfull) + (int64_t)b * a.vf_sB + (int64_t)h * a.vf_sH;
+            const int co = tid & 15, tl = tid >> 4;           // 8 channels per thread, 8 token lanes per CTA
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int t = lo + tl; t < t1; t += 8) {
+                int s0 = a.vf_start + (t - a.Tvq);
+                if (s0 >= a.vf_cap) s0 -= a.vf_cap;
+                const uint4 u = __ldg(reinterpret_cast<const uint4 *>(vf + (int64_t)s0 * a.vf_sT) + co);
+                const float p = sm.scores[t - t0];
+                const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __half22float2(h[k]);
+                    acc[2 * k] = fmaf(p, f.x, acc[2 * k]);
+                    acc[2 * k + 1] = fmaf(p, f.y, acc[2 * k + 1]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 16);   // the warp's two token lanes
+            if (lane < 16) {
+                float4 *dst = reinterpret_cast<float4 *>(sm.tailred + warp * kHeadDim + 8 * co);
+                dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- 4. finish / merge (same protocol as the generic kernel) ------------------------------------
+    float o = (sm.tailred[tid] + sm.tailred[kHeadDim + tid]) + (sm.tailred[2 * kHeadDim + tid] + sm.tailred[3 * kHeadDim + tid]);
+    if (t0 < min(t1, a.Tvq)) {                               // each warp left its packed-value partial at its region base
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w)
+            o += reinterpret_cast<const float *>(after_scores + w * warp_region_bytes<KB, VB>())[tid];
+    }
+    __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)h * a.o_sH;
+    if (n_splits == 1) {
+        out[tid] = __float2half_rn(o / l);
+        return;
+    }
+    constexpr int kPart = kHeadDim + 2;
+    float *part = parts + ((int64_t)s * n_splits + split) * kPart;
+    part[tid] = o;
+    if (tid == 0) { part[kHeadDim] = m; part[kHeadDim + 1] = l; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) sm.misc[8] = (atomicAdd(&counters[s], 1u) == (unsigned)(n_splits - 1)) ? 1.f : 0.f;
+    __syncthreads();
+    if (sm.misc[8] == 0.f) return;
+    __threadfence();
+    const float *base = parts + (int64_t)s * n_splits * kPart;
+    float M = -3.0e38f;
+    for (int i = 0; i < n_splits; ++i) M = fmaxf(M, __ldcg(base + i * kPart + kHeadDim));
+    float L = 0.f, acc = 0.f;
+    for (int i = 0; i < n_splits; ++i) {
+        const float w = __expf(__ldcg(base + i * kPart + kHeadDim) - M);
+        L = fmaf(__ldcg(base + i * kPart + kHeadDim + 1), w, L);
+        acc = fmaf(__ldcg(base + i * kPart + tid), w, acc);
+    }
+    out[tid] = __float2half_rn(acc / L);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The tensor-core path needs one query head per kv head, supported group sizes, 16-byte aligned and
+// row-contiguous packed tensors (cp.async granules), and a packed-value length that is a multiple of 16.
+bool mma_path_eligible(const kvq_attn_args &a) {
+    if (a.nh != a.nh_kv || a.D != kHeadDim) return false;
+    if (a.k_bits == 3) {
+        if (a.k_group != 11) return false;
+    } else if (a.k_group != 32 && a.k_group != 64 && a.k_group != 128) {
+        return false;
+    }
+    if (a.v_bits == 3) return false;
+    if (a.v_group != 32 && a.v_group != 64 && a.v_group != 128) return false;
+    if (a.Tvq % 32 != 0) return false;
+    auto al16 = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    if (a.T > a.Tkq && (!al16(a.kfull) || a.kf_sB % 8 || a.kf_sH % 8 || a.kf_sT % 8)) return false;
+    if (a.T > a.Tvq && (!al16(a.vfull) || a.vf_sB % 8 || a.vf_sH % 8 || a.vf_sT % 8)) return false;
+    if (a.Tkq > 0) {
+        if (!al16(a.kcode) || a.kc_sB % 4 || a.kc_sH % 4 || a.kc_sD % 4) return false;
+        if (!al16(a.kscale) || !al16(a.kmn) || a.ks_sB % 8 || a.ks_sH % 8 || a.ks_sD % 8) return false;
+    }
+    if (a.Tvq > 0) {
+        const int fv = fields_per_word(a.v_bits);
+        if (!al16(a.vcode) || a.vc_sB % 4 || a.vc_sH % 4 || a.vc_sT != kHeadDim / fv) return false;
+        if (!al16(a.vscale) || !al16(a.vmn) || a.vs_sB % 8 || a.vs_sH % 8 || a.vs_sT != kHeadDim / a.v_group) return false;
+    }
+    return true;
+}
+
+template <int KB, int VB>
+static int launch_mma(const kvq_attn_args &a, int chunk, int n_splits, float *parts, unsigned int *counters,
+                      cudaStream_t st) {
+    int n_scores = chunk < a.T ? chunk : a.T;
+    n_scores = (n_scores + 31) / 32 * 32;
+    const size_t smem = (size_t)n_scores * 4 + (size_t)kMmaWarps * warp_region_bytes<KB, VB>() +
+                        kMmaWarps * kHeadDim * 4 + kHeadDim * 2 + 16 * 4;
+    cudaError_t e = cudaFuncSetAttribute(decode_attn_mma_kernel<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         112 * 1024);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    const int64_t heads = (int64_t)a.B * a.nh;
+    decode_attn_mma_kernel<KB, VB><<<(unsigned)(heads * n_splits), kMmaThreads, smem, st>>>(a, chunk, n_splits, n_scores,
+                                                                                          parts, counters);
+    return check_launch();
+}
+
+int launch_decode_attn_mma(const kvq_attn_args &a, int chunk, int n_splits, float *parts, unsigned int *counters,
+                           cudaStream_t st) {
+#define KVQ_MMA_CASE(KB, VB) \
+    if (a.k_bits == KB && a.v_bits == VB) return launch_mma<KB, VB>(a, chunk, n_splits, parts, counters, st);
+    KVQ_MMA_CASE(4, 4) KVQ_MMA_CASE(4, 2) KVQ_MMA_CASE(4, 1)
+    KVQ_MMA_CASE(3, 4) KVQ_MMA_CASE(3, 2) KVQ_MMA_CASE(3, 1)
+    KVQ_MMA_CASE(2, 4) KVQ_MMA_CASE(2, 2) KVQ_MMA_CASE(2, 1)
+    KVQ_MMA_CASE(1, 4) KVQ_MMA_CASE(1, 2) KVQ_MMA_CASE(1, 1)
+#undef KVQ_MMA_CASE
+    return KVQ_ERR_UNSUPPORTED;
+}
+
+}  // namespace kvq

@@ -22,6 +22,24 @@ def _attend_gpu(c, q, dev, **kw):
                                c.k_group, c.v_bits, c.v_group, **kw).cpu().numpy()
 
 
+def _attend_cache(c, q, dev, round_scores=True):
+    """Same state loaded into the preallocated, aligned cache: this is the layout the tensor-core kernel takes."""
+    import kvmix_b200 as kv
+    T = c.kv_seq_len
+    pol = dict(residual_length=c.window) if c.window is not None else dict(k_residual_ratio=c.rk, v_residual_ratio=c.rv)
+    B, hkv = c.kfull.shape[0], c.kfull.shape[1]
+    dut = kv.KVmixLayerCache(B, hkv, 128, T + 64, c.k_bits, c.v_bits, c.v_group, device=dev,
+                             max_tail=max(c.kfull.shape[2], c.vfull.shape[2]) + 8, **pol)
+    dut.load_tuple(tuple(_t(x, dev) for x in (c.kcode, c.kfull, c.kscale, c.kmn, c.vcode, c.vfull, c.vscale, c.vmn))
+                   + (T,))
+    return dut.attend(_t(q, dev), round_scores=round_scores).cpu().numpy()
+
+
+def _both_paths(ref, q, dev):
+    assert_attn_parity(lambda rs: _attend_gpu(ref, q, dev, round_scores=rs), ref, q)
+    assert_attn_parity(lambda rs: _attend_cache(ref, q, dev, round_scores=rs), ref, q)
+
+
 def test_config1_micro(cuda):
     """Batch 1, 32 heads, ctx 1024, K4 per-channel / V2 per-token, group 32, fp16 window 128."""
     import kvmix_b200 as kv
@@ -36,8 +54,8 @@ def test_config1_micro(cuda):
     assert (kc.cpu().numpy() == ref.kcode).all() and (vc.cpu().numpy() == ref.vcode).all()
     for g, w in [(ks, ref.kscale), (km, ref.kmn), (vs, ref.vscale), (vm, ref.vmn)]:
         assert (g.cpu().numpy().view(np.uint16) == w.view(np.uint16)).all()
-    assert_attn_parity(lambda rs: _attend_gpu(ref, q, cuda, round_scores=rs), ref, q)
-    assert_attn_close(_attend_gpu(ref, q, cuda), ref.attend(q, ref_rounding=7))      # this case: inside 2e-3 of upstream
+    _both_paths(ref, q, cuda)
+    assert_attn_close(_attend_cache(ref, q, cuda), ref.attend(q, ref_rounding=7))    # this case: inside 2e-3 of upstream
 
 
 @pytest.mark.parametrize("kb,vb,G", [(4, 4, 32), (3, 2, 32), (2, 2, 32), (2, 1, 64), (4, 4, 64), (1, 2, 32), (3, 4, 128),
@@ -49,7 +67,7 @@ def test_bit_widths_groups_gqa(cuda, kb, vb, G, nh, hkv):
     q = make_q(kb, 2, nh)
     ref = RefLayerCache(kb, vb, G, residual_length=128)
     ref.prefill(k, v)
-    assert_attn_parity(lambda rs: _attend_gpu(ref, q, cuda, round_scores=rs), ref, q)
+    _both_paths(ref, q, cuda)
 
 
 def test_independent_boundaries_ratio_policy(cuda):
@@ -59,7 +77,7 @@ def test_independent_boundaries_ratio_policy(cuda):
     ref = RefLayerCache(3, 4, 32, k_residual_ratio=0.2, v_residual_ratio=0.3)
     ref.prefill(k, v)
     assert ref.tkq != ref.tvq
-    assert_attn_parity(lambda rs: _attend_gpu(ref, q, cuda, round_scores=rs), ref, q)
+    _both_paths(ref, q, cuda)
 
 
 def test_edge_cases_no_packed_part_and_tiny_context(cuda):
@@ -69,7 +87,7 @@ def test_edge_cases_no_packed_part_and_tiny_context(cuda):
         ref = RefLayerCache(4, 2, 32, residual_length=128)
         ref.prefill(k, v)
         assert ref.kcode is None and ref.vcode is None
-        assert_attn_parity(lambda rs: _attend_gpu(ref, q, cuda, round_scores=rs), ref, q)
+        _both_paths(ref, q, cuda)
 
 
 def test_fully_packed_keys_zero_tail(cuda):
@@ -79,7 +97,7 @@ def test_fully_packed_keys_zero_tail(cuda):
     ref = RefLayerCache(2, 4, 32, residual_length=0)
     ref.prefill(k, v)
     assert ref.kfull.shape[2] == 0 and ref.tkq == 256
-    assert_attn_parity(lambda rs: _attend_gpu(ref, q, cuda, round_scores=rs), ref, q)
+    _both_paths(ref, q, cuda)
 
 
 def test_split_merge_long_context_is_deterministic(cuda):
@@ -92,16 +110,17 @@ def test_split_merge_long_context_is_deterministic(cuda):
     a = _attend_gpu(ref, q, cuda)
     b = _attend_gpu(ref, q, cuda)
     assert (a.view(np.uint16) == b.view(np.uint16)).all()
-    assert_attn_parity(lambda rs: _attend_gpu(ref, q, cuda, round_scores=rs), ref, q)
+    _both_paths(ref, q, cuda)
 
 
 @pytest.mark.parametrize("policy", ["window", "ratio"])
 @pytest.mark.parametrize("kb,vb,G", [(4, 2, 32), (3, 2, 32), (2, 1, 64)])
-def test_cache_decode_loop_matches_glue(cuda, policy, kb, vb, G):
+@pytest.mark.parametrize("nh", [2, 4])      # 2 = one query head per kv head (tensor-core kernel), 4 = grouped queries
+def test_cache_decode_loop_matches_glue(cuda, policy, kb, vb, G, nh):
     """Prefill + 80 decode steps: the preallocated ring cache and upstream's cat-based protocol hold the
     same tokens in the same form at every step, and attention matches."""
     import kvmix_b200 as kv
-    B, hkv, nh, L, steps = 2, 2, 4, 300, 80
+    B, hkv, L, steps = 2, 2, 300, 80
     k, v = make_kv(21, B, hkv, L + steps)
     pol = dict(residual_length=128) if policy == "window" else dict(k_residual_ratio=0.2, v_residual_ratio=0.1)
     ref = RefLayerCache(kb, vb, G, **pol)
