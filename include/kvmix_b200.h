@@ -42,6 +42,7 @@ enum {
     KVQ_ERR_UNSUPPORTED = -11,/* outside what the kernels implement (see each call)  */
     KVQ_ERR_WORKSPACE = -12,  /* workspace missing or too small                      */
     KVQ_ERR_ALIGN = -13,      /* pointer or stride alignment                         */
+    KVQ_ERR_STATIC_SCRATCH = -14, /* problem needs more than KVQ_STATIC_SCRATCH_BYTES */
     KVQ_ERR_CUDA = -100       /* a CUDA call or launch failed                        */
 };
 
@@ -180,6 +181,36 @@ typedef struct {
 
 uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32_t T);
 int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream);
+
+/*
+ * kvq_decode_attn for callers that have no device memory to give.  (No counterpart in upstream KVmix:
+ * there every call allocates through torch.)
+ *
+ * Who needs it: a host that reaches this library over a foreign-function boundary (cgo, JNI, ctypes from
+ * a process without torch) owns no device allocator at all -- it only holds the cache pointers it was
+ * handed; and a serving engine that gives every free byte of HBM to its KV-cache pool at start-up cannot
+ * get a further cudaMalloc to succeed later, nor afford the device-wide synchronisation a cudaMalloc
+ * implies in the middle of a decode loop.  Neither can supply the split-partials workspace that
+ * kvq_decode_attn asks for.
+ *
+ * This variant takes the same arguments, ignores a->workspace / a->workspace_bytes, and keeps the split
+ * partials and per-head counters in a fixed KVQ_STATIC_SCRATCH_BYTES (8 MiB) array that is part of the
+ * library image: every GPU on which the library is loaded holds those 8 MiB until the process exits.
+ * It calls no cudaMalloc, cudaFree or any allocating routine.
+ *
+ *  - Limit: kvq_decode_attn_workspace_bytes(B, nh, T) must not exceed KVQ_STATIC_SCRATCH_BYTES, else
+ *    KVQ_ERR_STATIC_SCRATCH is returned and nothing is launched (8 MiB covers e.g. 32 heads at 131072
+ *    tokens, or 2048 heads at any length that needs one split).
+ *  - First call on each device: the device address of the array is looked up once per device, on the
+ *    first call made while that device is current (cudaGetSymbolAddress); make that first call before
+ *    starting any stream capture.
+ *  - The array is shared by every call on the device and keeps the previous call's contents; the call
+ *    zeroes the counters it needs itself.  Two calls that overlap on the GPU (different streams, or
+ *    different host threads) race on it: serialise them on one stream, or use kvq_decode_attn with a
+ *    workspace per stream.
+ */
+#define KVQ_STATIC_SCRATCH_BYTES (8u << 20)
+int kvq_decode_attn_static(const kvq_attn_args *a, kvq_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -36,6 +36,9 @@ extern "C" const char *kvq_error_string(int code) {
         case KVQ_ERR_UNSUPPORTED: return "configuration not supported by the sm_100a kernels";
         case KVQ_ERR_WORKSPACE: return "workspace missing or too small";
         case KVQ_ERR_ALIGN: return "pointer or stride alignment";
+        case KVQ_ERR_STATIC_SCRATCH:
+            return "problem too large for the built-in scratch (kvq_decode_attn_workspace_bytes exceeds KVQ_STATIC_SCRATCH_BYTES = 8 MiB): "
+                   "use kvq_decode_attn with a caller-provided workspace";
         case KVQ_ERR_CUDA: return "CUDA error";
         default: return "unknown error";
     }

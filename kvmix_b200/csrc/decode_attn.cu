@@ -330,3 +330,47 @@ extern "C" int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream) {
                                                                                    parts, counters);
     return check_launch();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant: the scratch lives in the library image.  The symbol below is a host-side
+// handle in host code, not a device address; its address on the current device is fetched once per
+// device with cudaGetSymbolAddress and cached.
+static __device__ __align__(256) unsigned char g_static_scratch[KVQ_STATIC_SCRATCH_BYTES];
+
+namespace kvq {
+constexpr int kMaxDevices = 64;
+static void *g_static_scratch_ptr[kMaxDevices];
+static int g_static_scratch_state[kMaxDevices];   // 0 = not looked up, 1 = ready
+
+static int static_scratch_for_current_device(void **out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (dev < 0 || dev >= kMaxDevices) return KVQ_ERR_UNSUPPORTED;
+    if (__atomic_load_n(&g_static_scratch_state[dev], __ATOMIC_ACQUIRE) != 1) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);    // device `dev` is current here
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (!p) return KVQ_ERR_CUDA;
+        g_static_scratch_ptr[dev] = p;                     // same value from every thread: benign if raced
+        __atomic_store_n(&g_static_scratch_state[dev], 1, __ATOMIC_RELEASE);
+    }
+    *out = g_static_scratch_ptr[dev];
+    return KVQ_OK;
+}
+}  // namespace kvq
+
+extern "C" int kvq_decode_attn_static(const kvq_attn_args *a, kvq_stream_t stream) {
+    using namespace kvq;
+    if (!a) return KVQ_ERR_NULL;
+    if (a->B > 0 && a->nh > 0 && a->T > 0 &&
+        kvq_decode_attn_workspace_bytes(a->B, a->nh, a->T) > (uint64_t)KVQ_STATIC_SCRATCH_BYTES)
+        return KVQ_ERR_STATIC_SCRATCH;
+    void *scratch = nullptr;
+    const int rc = static_scratch_for_current_device(&scratch);
+    if (rc != KVQ_OK) return rc;
+    kvq_attn_args b = *a;
+    b.workspace = scratch;
+    b.workspace_bytes = KVQ_STATIC_SCRATCH_BYTES;
+    return kvq_decode_attn(&b, stream);                    // zeroes the counters it uses on `stream`
+}
