@@ -177,8 +177,9 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    assert cfg.batch % world == 0, "global batch must divide across ranks"
-    B = cfg.batch // world
+    from kvmix_b200 import sharding
+    b_lo, b_hi = sharding.shard_batch(cfg.batch, world, rank)   # strong scaling: the global batch is split
+    B = b_hi - b_lo
     W, K = args.warmup, args.steps
     L, nh, hkv, D = cfg.n_layers, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
 

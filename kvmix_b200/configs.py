@@ -72,7 +72,7 @@ def synth_kv(batch, kv_heads, tokens, head_dim, device, seed, outliers=4, outlie
     g = torch.Generator(device=device).manual_seed(seed)
     k = torch.randn((batch, kv_heads, tokens, head_dim), generator=g, device=device, dtype=torch.float16)
     v = torch.randn((batch, kv_heads, tokens, head_dim), generator=g, device=device, dtype=torch.float16)
-    ch = torch.stack([torch.randperm(head_dim, generator=g, device=device)[:outliers] for _ in range(kv_heads)])
+    ch = torch.rand((kv_heads, head_dim), generator=g, device=device).argsort(dim=1)[:, :outliers]
     scale = torch.ones((kv_heads, head_dim), device=device, dtype=torch.float16)
     scale.scatter_(1, ch, outlier_scale)
     k.mul_(scale[None, :, None, :])

@@ -416,8 +416,8 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     // operand build: lane -> pair pi = lane & 15, column half ch = lane >> 4 (groups 2ch, 2ch+1)
     const int pi = lane & 15, ch = lane >> 4;
     const int bt0 = 16 * (pi >> 3) + 8 * ((pi >> 2) & 1) + (pi & 3), bt1 = bt0 + 4;      // the pair's tokens in the stage
-    const int g0 = min(2 * ch, ngv - 1), g1 = min(2 * ch + 1, ngv - 1);                  // clamped: dead columns are zeroed below
-    const float live0 = (2 * ch < ngv) ? 1.f : 0.f, live1 = (2 * ch + 1 < ngv) ? 1.f : 0.f;
+    // columns beyond the last channel group repeat that group: finite values in C columns nobody reads
+    const int g0 = min(2 * ch, ngv - 1), g1 = min(2 * ch + 1, ngv - 1);
     const uint32_t o00 = ring_s + G::SZ_OFF + (bt0 * ngv + g0) * 2, o01 = ring_s + G::SZ_OFF + (bt0 * ngv + g1) * 2;
     const uint32_t o10 = ring_s + G::SZ_OFF + (bt1 * ngv + g0) * 2, o11 = ring_s + G::SZ_OFF + (bt1 * ngv + g1) * 2;
     const uint32_t pb_wr = pb_s + (pi * 8 + 4 * ch) * 4;
@@ -464,14 +464,14 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
         // ---- B operands for the stage: 16 token pairs x 8 columns -----------------------------------
         {
             const float p0 = pp[bt0], p1 = pp[bt1];
-            const float s00 = live0 * __half2float(__ushort_as_half((unsigned short)lds16(o00 + st)));
-            const float s01 = live1 * __half2float(__ushort_as_half((unsigned short)lds16(o01 + st)));
-            const float s10 = live0 * __half2float(__ushort_as_half((unsigned short)lds16(o10 + st)));
-            const float s11 = live1 * __half2float(__ushort_as_half((unsigned short)lds16(o11 + st)));
-            const float z00 = live0 * __half2float(__ushort_as_half((unsigned short)lds16(o00 + st + 256)));
-            const float z01 = live1 * __half2float(__ushort_as_half((unsigned short)lds16(o01 + st + 256)));
-            const float z10 = live0 * __half2float(__ushort_as_half((unsigned short)lds16(o10 + st + 256)));
-            const float z11 = live1 * __half2float(__ushort_as_half((unsigned short)lds16(o11 + st + 256)));
+            const float s00 = __half2float(__ushort_as_half((unsigned short)lds16(o00 + st)));
+            const float s01 = __half2float(__ushort_as_half((unsigned short)lds16(o01 + st)));
+            const float s10 = __half2float(__ushort_as_half((unsigned short)lds16(o10 + st)));
+            const float s11 = __half2float(__ushort_as_half((unsigned short)lds16(o11 + st)));
+            const float z00 = __half2float(__ushort_as_half((unsigned short)lds16(o00 + st + 256)));
+            const float z01 = __half2float(__ushort_as_half((unsigned short)lds16(o01 + st + 256)));
+            const float z10 = __half2float(__ushort_as_half((unsigned short)lds16(o10 + st + 256)));
+            const float z11 = __half2float(__ushort_as_half((unsigned short)lds16(o11 + st + 256)));
             // columns 4ch .. 4ch+3 = (p*scale_g0, p*mid_g0, p*scale_g1, p*mid_g1), each a half2 over the token pair;
             // mid = zero + MID*scale is the midpoint of the group: codes are used as (code - MID)
             const uint32_t c0 = as_u32(__floats2half2_rn(p0 * s00, p1 * s10));

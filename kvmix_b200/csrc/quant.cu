@@ -31,6 +31,21 @@ __device__ __forceinline__ int round_code(float n, int emax) {
     return max(0, min(k, emax));
 }
 
+// Code of one element, bit-identical to clamp(roundf((v - lo) / sc), 0, emax) with IEEE division, without
+// paying for a division per element: y = (v - lo) * rinv with rinv = fl(1/sc) is within 3e-6 of the true
+// quotient, and so is the IEEE quotient; unless y lies within 1e-4 of a rounding boundary (k + 0.5) both
+// round to the same integer.  The rare boundary cases (and NaN from a constant group, 0 * inf) take the
+// exact division.
+__device__ __forceinline__ int quant_code(float v, float lo, float sc, float rinv, int emax) {
+    const float a = v - lo;
+    const float y = a * rinv;
+    int k = __float2int_rz(y);
+    const float d = y - (float)k;
+    if (!(fabsf(d - 0.5f) >= 1e-4f)) return round_code(a / sc, emax);   // near a tie, or NaN
+    k += (d >= 0.5f) ? 1 : 0;
+    return max(0, min(k, emax));
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
@@ -99,15 +114,15 @@ __global__ void __launch_bounds__(256) quant_contig_kernel(const T *__restrict__
     }
     constexpr int QMAX = (1 << BITS) - 1;
     const float sc = (hi - lo) / (float)QMAX;
+    const float rinv = 1.0f / sc;
     uint32_t word = 0;
 #pragma unroll
     for (int i = 0; i < E; ++i) {
-        const float n = (v[i] - lo) / sc;
         if constexpr (BITS == 3) {
-            const int q = round_code(n, i < 10 ? 7 : 3);
+            const int q = quant_code(v[i], lo, sc, rinv, i < 10 ? 7 : 3);
             word |= (uint32_t)q << (i < 10 ? 3 * i : 30);
         } else {
-            word |= (uint32_t)round_code(n, QMAX) << (BITS * i);
+            word |= (uint32_t)quant_code(v[i], lo, sc, rinv, QMAX) << (BITS * i);
         }
     }
     if (active) {
@@ -167,20 +182,20 @@ __global__ void __launch_bounds__(256) quant_strided_kernel(const __half *__rest
             lo1 = fminf(lo1, f.y); hi1 = fmaxf(hi1, f.y);
         }
         const float sc0 = (hi0 - lo0) / (float)QMAX, sc1 = (hi1 - lo1) / (float)QMAX;
+        const float ri0 = 1.0f / sc0, ri1 = 1.0f / sc1;
 #pragma unroll
         for (int w = 0; w < C::WPG; ++w) {
             uint32_t w0 = 0, w1 = 0;
 #pragma unroll
             for (int i = 0; i < C::FPI; ++i) {
                 float2 f = __half22float2(raw[w * C::FPI + i]);
-                const float n0 = (f.x - lo0) / sc0, n1 = (f.y - lo1) / sc1;
                 if constexpr (BITS == 3) {
                     const int em = i < 10 ? 7 : 3, sh = i < 10 ? 3 * i : 30;
-                    w0 |= (uint32_t)round_code(n0, em) << sh;
-                    w1 |= (uint32_t)round_code(n1, em) << sh;
+                    w0 |= (uint32_t)quant_code(f.x, lo0, sc0, ri0, em) << sh;
+                    w1 |= (uint32_t)quant_code(f.y, lo1, sc1, ri1, em) << sh;
                 } else {
-                    w0 |= (uint32_t)round_code(n0, QMAX) << (BITS * i);
-                    w1 |= (uint32_t)round_code(n1, QMAX) << (BITS * i);
+                    w0 |= (uint32_t)quant_code(f.x, lo0, sc0, ri0, QMAX) << (BITS * i);
+                    w1 |= (uint32_t)quant_code(f.y, lo1, sc1, ri1, QMAX) << (BITS * i);
                 }
             }
             s_code[(2 * pair) * C::WPAD + g * C::WPG + w] = (int32_t)w0;
