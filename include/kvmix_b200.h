@@ -93,6 +93,30 @@ typedef struct {
 int kvq_quant_lastdim(const kvq_quant_args *a, kvq_stream_t stream);
 
 /*
+ * Append one token's keys and values (fp16, after RoPE) to the fp16 tails of the cache, in one launch.
+ * Replaces the two torch.cat calls upstream makes per layer and step (models/modeling_llama_KVmix.py:111-112)
+ * without moving the old tail: row `k_slot` of kfull and row `v_slot` of vfull are overwritten.
+ *   k_new, v_new [B, Hkv, D] fp16, strides kn_sB, kn_sH / vn_sB, vn_sH (D contiguous)
+ *   kfull, vfull [B, Hkv, cap, D] fp16, strides *_sB, *_sH, *_sT
+ * D must be a multiple of 8 and all rows 16-byte aligned.
+ */
+typedef struct {
+    int32_t B, Hkv, D;
+    const void *k_new;
+    int64_t kn_sB, kn_sH;
+    const void *v_new;
+    int64_t vn_sB, vn_sH;
+    void *kfull;
+    int64_t kf_sB, kf_sH, kf_sT;
+    int32_t k_slot;
+    void *vfull;
+    int64_t vf_sB, vf_sH, vf_sT;
+    int32_t v_slot;
+} kvq_append_args;
+
+int kvq_append_kv(const kvq_append_args *a, kvq_stream_t stream);
+
+/*
  * Dequantising mat-vec, M = 1.
  * Replaces quantized_gemm, upstream quant_cuda/csrc/dequantization_gemv_cuda.cu:127-248 (kernel
  * :7-124), reading the caller's layout directly (upstream first transposes codes, scales and

@@ -30,6 +30,14 @@ class GemvArgs(C.Structure):
                 ("group", i32), ("bits", i32)]
 
 
+class AppendArgs(C.Structure):
+    _fields_ = [("B", i32), ("Hkv", i32), ("D", i32),
+                ("k_new", vp), ("kn_sB", i64), ("kn_sH", i64),
+                ("v_new", vp), ("vn_sB", i64), ("vn_sH", i64),
+                ("kfull", vp), ("kf_sB", i64), ("kf_sH", i64), ("kf_sT", i64), ("k_slot", i32),
+                ("vfull", vp), ("vf_sB", i64), ("vf_sH", i64), ("vf_sT", i64), ("v_slot", i32)]
+
+
 class AttnArgs(C.Structure):
     _fields_ = [("B", i32), ("nh", i32), ("nh_kv", i32), ("D", i32),
                 ("T", i32), ("Tkq", i32), ("Tvq", i32),
@@ -68,6 +76,8 @@ def lib():
         L.kvq_features_per_int.argtypes = [C.c_int]
         L.kvq_quant_lastdim.restype = C.c_int
         L.kvq_quant_lastdim.argtypes = [C.POINTER(QuantArgs), vp]
+        L.kvq_append_kv.restype = C.c_int
+        L.kvq_append_kv.argtypes = [C.POINTER(AppendArgs), vp]
         L.kvq_gemv.restype = C.c_int
         L.kvq_gemv.argtypes = [C.POINTER(GemvArgs), vp]
         L.kvq_decode_attn.restype = C.c_int
@@ -81,7 +91,7 @@ def lib():
 
 
 EXPORTS = ["kvq_version", "kvq_error_string", "kvq_last_cuda_error", "kvq_features_per_int",
-           "kvq_quant_lastdim", "kvq_gemv", "kvq_decode_attn", "kvq_decode_attn_workspace_bytes",
+           "kvq_quant_lastdim", "kvq_append_kv", "kvq_gemv", "kvq_decode_attn", "kvq_decode_attn_workspace_bytes",
            "kvq_decode_attn_static"]
 
 

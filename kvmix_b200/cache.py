@@ -16,11 +16,13 @@ copies.  The policy deciding *when* tokens are due is upstream's (:115-129, :152
 RoPE and ``o_proj``: it takes and returns the 9-tuple itself (contiguous tensors in upstream's
 layout), calling the same kernels.
 """
+import ctypes as C
 import math
 
 import torch
 
-from . import ops
+from . import _lib, ops
+from ._lib import AppendArgs, AttnArgs
 from .ops import features_per_int
 
 
@@ -70,6 +72,21 @@ class KVmixLayerCache:
         self.v_cap = _round_up(max_tail + 1, self.v_group)
         self.kfull = torch.empty((B, H, self.k_cap, D), dtype=torch.float16, device=dev)
         self.vfull = torch.empty((B, H, self.v_cap, D), dtype=torch.float16, device=dev)
+        # argument blocks of the two per-step launches, filled once; a step only patches what changes
+        kf, vf = self.kfull, self.vfull
+        self._app = AppendArgs(B, H, D, 0, 0, 0, 0, 0, 0, kf.data_ptr(), kf.stride(0), kf.stride(1), kf.stride(2), 0,
+                               vf.data_ptr(), vf.stride(0), vf.stride(1), vf.stride(2), 0)
+        kc, ks, vc, vs = self.kcode, self.kscale, self.vcode, self.vscale
+        self._att = AttnArgs(B, 0, H, D, 0, 0, 0, k_bits, self.k_group, v_bits, self.v_group, 1, 1.0 / math.sqrt(D),
+                             0, 0, 0, 0, 0, 0,
+                             kc.data_ptr(), kc.stride(0), kc.stride(1), kc.stride(2),
+                             ks.data_ptr(), self.kmn.data_ptr(), ks.stride(0), ks.stride(1), ks.stride(2),
+                             kf.data_ptr(), kf.stride(0), kf.stride(1), kf.stride(2), self.k_cap, 0,
+                             vc.data_ptr(), vc.stride(0), vc.stride(1), vc.stride(2),
+                             vs.data_ptr(), self.vmn.data_ptr(), vs.stride(0), vs.stride(1), vs.stride(2),
+                             vf.data_ptr(), vf.stride(0), vf.stride(1), vf.stride(2), self.v_cap, 0, 0, 0)
+        self._ws = {}
+        self._lib = _lib.lib()
         self.reset()
 
     def reset(self):
@@ -135,10 +152,15 @@ class KVmixLayerCache:
             raise RuntimeError("cache capacity exceeded")
         if self.k_len + 1 > self.k_cap or self.v_len + 1 > self.v_cap:
             raise RuntimeError("fp16 tail larger than the ring capacity (raise max_tail)")
-        ks = (self.k_start + self.k_len) % self.k_cap
-        vs = (self.v_start + self.v_len) % self.v_cap
-        self.kfull[:, :, ks:ks + 1].copy_(k_new)
-        self.vfull[:, :, vs:vs + 1].copy_(v_new)
+        a = self._app
+        if k_new.stride(3) != 1 or v_new.stride(3) != 1 or k_new.dtype != torch.float16 or v_new.dtype != torch.float16:
+            k_new, v_new = k_new.to(torch.float16).contiguous(), v_new.to(torch.float16).contiguous()
+        a.k_new, a.kn_sB, a.kn_sH = k_new.data_ptr(), k_new.stride(0), k_new.stride(1)
+        a.v_new, a.vn_sB, a.vn_sH = v_new.data_ptr(), v_new.stride(0), v_new.stride(1)
+        a.k_slot = (self.k_start + self.k_len) % self.k_cap
+        a.v_slot = (self.v_start + self.v_len) % self.v_cap
+        _lib.check(self._lib.kvq_append_kv(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        ops.LAUNCHES[0] += 1
         self.k_len += 1
         self.v_len += 1
         self.kv_seq_len += 1
@@ -147,10 +169,30 @@ class KVmixLayerCache:
     # -- attention -----------------------------------------------------------------------------------
     def attend(self, q, out=None, round_scores=True):
         """q: [B,nh,1,D] fp16 -> [B,nh,1,D] fp16 over everything cached (upstream :170-211)."""
-        return ops.decode_attention(q, self.kcode, self.kscale, self.kmn, self.kfull, self.vcode, self.vscale,
-                                    self.vmn, self.vfull, self.k_bits, self.k_group, self.v_bits, self.v_group,
-                                    Tkq=self.tkq, Tvq=self.tvq, Rk=self.k_len, Rv=self.v_len,
-                                    kf_start=self.k_start, vf_start=self.v_start, round_scores=round_scores, out=out)
+        B, nh, M, D = q.shape
+        if M != 1 or B != self.B or D != self.D or not q.is_cuda:
+            raise RuntimeError("attend takes q [B, nh, 1, D] on the cache's device")
+        if self.tkq + self.k_len != self.tvq + self.v_len:
+            _lib.check(-9)
+        if q.stride(3) != 1 or q.dtype != torch.float16:
+            q = q.to(torch.float16).contiguous()
+        if out is None:
+            out = torch.empty((B, nh, 1, D), dtype=torch.float16, device=q.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        ws = self._ws.get((nh, stream))
+        if ws is None:
+            need = int(self._lib.kvq_decode_attn_workspace_bytes(B, nh, self.max_tokens))
+            ws = self._ws[(nh, stream)] = torch.empty(need, dtype=torch.uint8, device=q.device)
+        a = self._att
+        a.nh, a.T, a.Tkq, a.Tvq = nh, self.tkq + self.k_len, self.tkq, self.tvq
+        a.round_scores = int(bool(round_scores))
+        a.q, a.q_sB, a.q_sH = q.data_ptr(), q.stride(0), q.stride(1)
+        a.out, a.o_sB, a.o_sH = out.data_ptr(), out.stride(0), out.stride(1)
+        a.kf_start, a.vf_start = self.k_start, self.v_start
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        _lib.check(self._lib.kvq_decode_attn(C.byref(a), C.c_void_p(stream)))
+        ops.LAUNCHES[0] += 1
+        return out
 
     def decode_step(self, q, k_new, v_new, out=None):
         self.append(k_new, v_new)
