@@ -29,6 +29,11 @@ SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.acti
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
 
+# DRAM traffic per (sequence, head) unit of one fused-attention launch, dram__bytes_read+write from the ncu
+# captures summarised in profiles/decode_attn_mma_kernel_B16_ctx4096.md (B=16 case; traffic is proportional to units).
+NCU_TRAFFIC_PER_UNIT = {(4, 4): 737.5e3, (3, 2): 660.0e3, (2, 2): 470.7e3}
+
+
 def measured_peak_gbs():
     for p in (os.path.join(ROOT, "MEASURED_PEAKS.json"), "/root/repo/MEASURED_PEAKS.json"):
         if os.path.exists(p):
@@ -297,7 +302,10 @@ def main():
                        "parallelism": f"batch-sharded x{world}, no data-path collective"},
             "roofline": {"bound": "hbm", "kernel": "decode_attn_mma_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
-                         "peak_source": peak_src, "traffic": None,
+                         "peak_source": peak_src,
+                         "traffic": (sum(NCU_TRAFFIC_PER_UNIT.get((q["k_bits"], q["v_bits"]), float("nan"))
+                                         for q in cfg.quant_bits.values()) / L * B * nh),
+                         "traffic_note": "bytes per launch (layer average), ncu dram read+write of a B=16 capture scaled by units",
                          "bytes_per_launch": attn_bytes_all / max(1, n_attn),
                          "us_per_launch": attn_ms_all * 1e3 / max(1, n_attn), "launches_timed": n_attn,
                          "attention_share_of_step": attn_ms_all / ms_total},
