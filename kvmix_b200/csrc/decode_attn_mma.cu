@@ -195,9 +195,15 @@ struct MmaSmem {
 // q . K^T over packed keys for tokens [t0, hi) (t0 is a multiple of 1024, or 352 for 3-bit keys).
 // Scores (already multiplied by softmax_scale) go to sm.scores[t - t0].  Warps work independently:
 // warp w takes warp tiles w, w+4, ... and streams their code words through its own ring.
+__device__ __forceinline__ void qk_tail_mma(const kvq_attn_args &a, const __half *kf, const MmaSmem &sm, int t0,
+                                            int lo, int t1);
+
+// If the split also holds fp16 tail keys (tail_lo < t1) they are scored right after the first code stages
+// have been issued, so the tail's global-load latency overlaps the ring fill.
 template <int KB>
 __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int32_t *kc, const __half *ks,
-                                              const __half *kz, const MmaSmem &sm, int t0, int hi) {
+                                              const __half *kz, const MmaSmem &sm, int t0, int hi,
+                                              const __half *kf, int tail_lo, int t1) {
     using G = KGeom<KB>;
     using F = Fields<KB>;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
@@ -205,7 +211,10 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     const int n_words = a.Tkq / G::FPI;                       // valid code words per channel row
     const int n_tiles = (hi - t0 + G::WT - 1) / G::WT;
     const int my_tiles = (n_tiles - warp + kMmaWarps - 1) / kMmaWarps;   // tiles warp, warp+4, ...
-    if (my_tiles <= 0) return;
+    if (my_tiles <= 0) {
+        if (tail_lo < t1) qk_tail_mma(a, kf, sm, t0, tail_lo, t1);
+        return;
+    }
 
     const int kc_sD = (int)a.kc_sD, ks_sD = (int)a.ks_sD;
     // ---- per-lane constants --------------------------------------------------------------------
@@ -216,6 +225,8 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     const uint32_t frag_s = ring_s + (2 * tig) * G::RS + g * (4 * G::WPL);     // + slot*STAGE + (16k + rr)*RS
     const int gw = (g * G::TPO) / Gk;                                          // group of this octet inside the warp tile
     const uint32_t szl_s = sz_s + ((2 * tig) * 8 + gw) * 2;                    // + (16 ksx + {0,1,8,9}) * 16 [+ 2048 for zero]
+    // ldmatrix.x4 row addresses: lanes 0-7 scale rows 16ksx+0..7, 8-15 scale rows +8..15, 16-31 the same of the zero tile
+    const uint32_t ldm_s = sz_s + (((lane >> 3) & 1) * 8 + (lane & 7)) * 16 + (lane >> 4) * 2048;
     const uint32_t q_s = smem_u32(sm.q) + (2 * tig) * 2;                       // + 32 ksx [+16]
     const int ngw = (G::WT + Gk - 1) / Gk;                                     // groups per warp tile: 8 / 4 / 2
     const uint32_t szcp_dst = sz_s + lane * 16;                                // + i*512
@@ -253,6 +264,7 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     cp_async_commit();
     issue_stage(tb_cur, ok_cur, 2);
     cp_async_commit();
+    if (tail_lo < t1) qk_tail_mma(a, kf, sm, t0, tail_lo, t1);
 
     const uint32_t ones = 0x3c003c00u;
     for (int j = 0; j < my_tiles; ++j) {
@@ -275,10 +287,21 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
 #pragma unroll
         for (int ksx = 0; ksx < 8; ++ksx) {
             const __half2 q01 = as_h2(lds32(q_s + 32 * ksx)), q89 = as_h2(lds32(q_s + 32 * ksx + 16));
-            const uint32_t so = szl_s + ksx * 256;
-            const __half2 s01 = as_h2(lds16(so) | (lds16(so + 16) << 16)), s89 = as_h2(lds16(so + 128) | (lds16(so + 144) << 16));
-            const __half2 z01 = as_h2(lds16(so + 2048) | (lds16(so + 2064) << 16));
-            const __half2 z89 = as_h2(lds16(so + 2176) | (lds16(so + 2192) << 16));
+            __half2 s01, s89, z01, z89;
+            if (ngw == 8) {
+                // the tile rows are 8 groups x fp16 = one 8x8 matrix per 8 channels: a transposing ldmatrix hands
+                // lane (g, tig) exactly {row 2tig, row 2tig+1} x column g, i.e. its B-fragment pairs, in one go
+                uint32_t r0, r1, r2, r3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(ldm_s + ksx * 256));
+                s01 = as_h2(r0); s89 = as_h2(r1); z01 = as_h2(r2); z89 = as_h2(r3);
+            } else {
+                const uint32_t so = szl_s + ksx * 256;
+                s01 = as_h2(lds16(so) | (lds16(so + 16) << 16));
+                s89 = as_h2(lds16(so + 128) | (lds16(so + 144) << 16));
+                z01 = as_h2(lds16(so + 2048) | (lds16(so + 2064) << 16));
+                z89 = as_h2(lds16(so + 2176) | (lds16(so + 2192) << 16));
+            }
             const __half2 b01 = __hmul2(q01, s01), b89 = __hmul2(q89, s89);
             const __half2 y01 = __hmul2(q01, z01), y89 = __hmul2(q89, z89);
             bq[ksx][0] = as_u32(b01);
@@ -379,7 +402,9 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
 // token pairs x 8 columns, half2 per pair) in a small tile, then every lane reads its two B registers
 // per k-step with one 32-bit load each.  Returns this warp's 128 partial channel sums in its own
 // ring region (float [128] at the region base).
-template <int VB>
+// MODE 1 only issues the first stages (called before the softmax, whose latency then hides the ring fill);
+// MODE 2 continues after such a call; MODE 0 does both.
+template <int VB, int MODE>
 __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int32_t *vc, const __half *vs,
                                               const __half *vz, const MmaSmem &sm, int t0, int hi) {
     using G = VGeom<VB>;
@@ -394,7 +419,8 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     const int my_blocks = (n_blocks - warp + kMmaWarps - 1) / kMmaWarps;
     float *my_red = reinterpret_cast<float *>(sm.ring);
     if (my_blocks <= 0) {
-        for (int i = lane; i < kHeadDim; i += 32) my_red[i] = 0.f;
+        if (MODE != 1)
+            for (int i = lane; i < kHeadDim; i += 32) my_red[i] = 0.f;
         return;
     }
 
@@ -451,8 +477,15 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
     const uint32_t ones = 0x3c003c00u;
 
+    if (MODE != 2) {
 #pragma unroll
-    for (int q = 0; q < G::P; ++q) { issue_stage(q * G::STAGE_BYTES); cp_async_commit(); }
+        for (int q = 0; q < G::P; ++q) { issue_stage(q * G::STAGE_BYTES); cp_async_commit(); }
+        if (MODE == 1) return;
+    } else {                                                   // those stages are already in flight
+        to_issue -= G::P;
+        src_codes += G::P * codes_step;
+        src_sz += G::P * sz_step;
+    }
 
     uint32_t st = 0, issue_st = G::P * G::STAGE_BYTES;         // byte offsets of the slot being read / filled
     const float *pp = sm.scores + warp * G::TPS;               // p of this warp's current block
@@ -605,14 +638,18 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
             const int32_t *kc = a.kcode + (int64_t)b * a.kc_sB + (int64_t)h * a.kc_sH;
             const __half *ks = static_cast<const __half *>(a.kscale) + (int64_t)b * a.ks_sB + (int64_t)h * a.ks_sH;
             const __half *kz = static_cast<const __half *>(a.kmn) + (int64_t)b * a.ks_sB + (int64_t)h * a.ks_sH;
-            qk_packed_mma<KB>(a, kc, ks, kz, sm, t0, hi);
-        }
-        const int lo = max(t0, a.Tkq);
-        if (lo < t1) {
             const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)h * a.kf_sH;
-            qk_tail_mma(a, kf, sm, t0, lo, t1);
+            qk_packed_mma<KB>(a, kc, ks, kz, sm, t0, hi, kf, max(t0, a.Tkq), t1);
+        } else if (t0 < t1) {
+            const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)h * a.kf_sH;
+            qk_tail_mma(a, kf, sm, t0, t0, t1);
         }
     }
+    const int32_t *vc = a.vcode + (int64_t)b * a.vc_sB + (int64_t)h * a.vc_sH;
+    const __half *vs = static_cast<const __half *>(a.vscale) + (int64_t)b * a.vs_sB + (int64_t)h * a.vs_sH;
+    const __half *vz = static_cast<const __half *>(a.vmn) + (int64_t)b * a.vs_sB + (int64_t)h * a.vs_sH;
+    const int v_hi = min(t1, a.Tvq);
+    if (t0 < v_hi) pv_packed_mma<VB, 1>(a, vc, vs, vz, sm, t0, v_hi);   // start filling this warp's value ring now
     __syncthreads();
 
     // ---- 2. softmax numerators ------------------------------------------------------------------
@@ -636,13 +673,7 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
 
     // ---- 3. p.V -----------------------------------------------------------------------------------
     {
-        const int hi = min(t1, a.Tvq);
-        if (t0 < hi) {
-            const int32_t *vc = a.vcode + (int64_t)b * a.vc_sB + (int64_t)h * a.vc_sH;
-            const __half *vs = static_cast<const __half *>(a.vscale) + (int64_t)b * a.vs_sB + (int64_t)h * a.vs_sH;
-            const __half *vz = static_cast<const __half *>(a.vmn) + (int64_t)b * a.vs_sB + (int64_t)h * a.vs_sH;
-            pv_packed_mma<VB>(a, vc, vs, vz, sm, t0, hi);
-        }
+        if (t0 < v_hi) pv_packed_mma<VB, 2>(a, vc, vs, vz, sm, t0, v_hi);
         const int lo = max(t0, a.Tvq);
         if (lo < t1) {
             const __half *vf = static_cast<const __half *>(a.vfull) + (int64_t)b * a.vf_sB + (int64_t)h * a.vf_sH;

@@ -72,16 +72,19 @@ __device__ __forceinline__ float stored_scale(float range, float quotient, int b
 template <int BITS, typename T>
 __global__ void __launch_bounds__(256) quant_contig_kernel(const T *__restrict__ x, int32_t *__restrict__ code,
                                                            T *__restrict__ scale, T *__restrict__ mn, QuantDims d,
-                                                           int tpg, bool vec_ok) {
+                                                           int tpg, bool vec_ok, bool linear) {
     constexpr int E = fields_per_word(BITS);
-    const int64_t words_per_row = d.S / E;
-    const int64_t total = d.B * d.H * d.A * words_per_row;
-    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // blockIdx.y = (b, h); inside a (b, h) slab words are numbered linearly (32-bit index arithmetic)
+    const int words_per_row = (int)(d.S / E);
+    const int total = (int)d.A * words_per_row;
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
     const bool active = idx < total;
     if (!active) idx = total - 1;  // keep the lane alive for the shuffles
-    const int64_t row = idx / words_per_row, w = idx % words_per_row;
-    const int64_t a = row % d.A, h = (row / d.A) % d.H, b = row / (d.A * d.H);
-    const T *px = x + b * d.x_sB + h * d.x_sH + a * d.x_sA + w * E;
+    const int b = blockIdx.y / (int)d.H, h = blockIdx.y % (int)d.H;
+    int a, w;
+    if (linear) { a = 0; w = idx; }                      // rows of the slab are back to back in x, code and scale
+    else { a = idx / words_per_row; w = idx - a * words_per_row; }
+    const T *px = x + b * d.x_sB + h * d.x_sH + a * d.x_sA + (int64_t)w * E;
 
     float v[E];
     if constexpr (sizeof(T) == 2 && (E % 8 == 0)) {
@@ -127,8 +130,8 @@ __global__ void __launch_bounds__(256) quant_contig_kernel(const T *__restrict__
     }
     if (active) {
         code[b * d.c_sB + h * d.c_sH + a * d.c_sA + w] = (int32_t)word;
-        if ((w % tpg) == 0) {
-            const int64_t zo = b * d.z_sB + h * d.z_sH + a * d.z_sA + w / tpg;
+        if ((w & (tpg - 1)) == 0) {                           // tpg is a power of two
+            const int64_t zo = b * d.z_sB + h * d.z_sH + a * d.z_sA + (w >> (__ffs(tpg) - 1));
             scale[zo] = from_f32<T>(stored_scale<QMAX>(hi - lo, sc, d.by_div));
             mn[zo] = from_f32<T>(lo);
         }
@@ -165,41 +168,50 @@ __global__ void __launch_bounds__(256) quant_strided_kernel(const __half *__rest
     const __half *px = x + b * d.x_sB + h * d.x_sH + (a0 + 2 * pair);
     constexpr int QMAX = (1 << BITS) - 1;
 
+    constexpr int CH = G > 32 ? 32 : G;                       // tokens held in registers at a time
+    constexpr int NCH = G / CH;
+    constexpr int WPCH = CH / C::FPI;                         // words per chunk (1 for the 11-token group)
     for (int g = slot; g < groups_here; g += 4) {
         const __half *pg = px + (g0 + g) * G * d.x_sS;
-        __half2 raw[G];
+        __half2 raw[CH];
+        float lo0 = 3.402823466e+38f, hi0 = -3.402823466e+38f, lo1 = lo0, hi1 = hi0;
+#pragma unroll 1
+        for (int c = 0; c < NCH; ++c) {
 #pragma unroll
-        for (int i = 0; i < G; ++i) raw[i] = __ldg(reinterpret_cast<const __half2 *>(pg + i * d.x_sS));
-        float lo0, hi0, lo1, hi1;
-        {
-            float2 f = __half22float2(raw[0]);
-            lo0 = hi0 = f.x; lo1 = hi1 = f.y;
-        }
+            for (int i = 0; i < CH; ++i) raw[i] = __ldg(reinterpret_cast<const __half2 *>(pg + (int64_t)(c * CH + i) * d.x_sS));
 #pragma unroll
-        for (int i = 1; i < G; ++i) {
-            float2 f = __half22float2(raw[i]);
-            lo0 = fminf(lo0, f.x); hi0 = fmaxf(hi0, f.x);
-            lo1 = fminf(lo1, f.y); hi1 = fmaxf(hi1, f.y);
+            for (int i = 0; i < CH; ++i) {
+                const float2 f = __half22float2(raw[i]);
+                lo0 = fminf(lo0, f.x); hi0 = fmaxf(hi0, f.x);
+                lo1 = fminf(lo1, f.y); hi1 = fmaxf(hi1, f.y);
+            }
         }
         const float sc0 = (hi0 - lo0) / (float)QMAX, sc1 = (hi1 - lo1) / (float)QMAX;
         const float ri0 = 1.0f / sc0, ri1 = 1.0f / sc1;
+#pragma unroll 1
+        for (int c = 0; c < NCH; ++c) {
+            if (NCH > 1) {                                    // long groups: second pass over the chunk (cache hit)
 #pragma unroll
-        for (int w = 0; w < C::WPG; ++w) {
-            uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-            for (int i = 0; i < C::FPI; ++i) {
-                float2 f = __half22float2(raw[w * C::FPI + i]);
-                if constexpr (BITS == 3) {
-                    const int em = i < 10 ? 7 : 3, sh = i < 10 ? 3 * i : 30;
-                    w0 |= (uint32_t)quant_code(f.x, lo0, sc0, ri0, em) << sh;
-                    w1 |= (uint32_t)quant_code(f.y, lo1, sc1, ri1, em) << sh;
-                } else {
-                    w0 |= (uint32_t)quant_code(f.x, lo0, sc0, ri0, QMAX) << (BITS * i);
-                    w1 |= (uint32_t)quant_code(f.y, lo1, sc1, ri1, QMAX) << (BITS * i);
-                }
+                for (int i = 0; i < CH; ++i) raw[i] = __ldg(reinterpret_cast<const __half2 *>(pg + (int64_t)(c * CH + i) * d.x_sS));
             }
-            s_code[(2 * pair) * C::WPAD + g * C::WPG + w] = (int32_t)w0;
-            s_code[(2 * pair + 1) * C::WPAD + g * C::WPG + w] = (int32_t)w1;
+#pragma unroll
+            for (int w = 0; w < WPCH; ++w) {
+                uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+                for (int i = 0; i < C::FPI; ++i) {
+                    const float2 f = __half22float2(raw[w * C::FPI + i]);
+                    if constexpr (BITS == 3) {
+                        const int em = i < 10 ? 7 : 3, sh = i < 10 ? 3 * i : 30;
+                        w0 |= (uint32_t)quant_code(f.x, lo0, sc0, ri0, em) << sh;
+                        w1 |= (uint32_t)quant_code(f.y, lo1, sc1, ri1, em) << sh;
+                    } else {
+                        w0 |= (uint32_t)quant_code(f.x, lo0, sc0, ri0, QMAX) << (BITS * i);
+                        w1 |= (uint32_t)quant_code(f.y, lo1, sc1, ri1, QMAX) << (BITS * i);
+                    }
+                }
+                s_code[(2 * pair) * C::WPAD + g * C::WPG + c * WPCH + w] = (int32_t)w0;
+                s_code[(2 * pair + 1) * C::WPAD + g * C::WPG + c * WPCH + w] = (int32_t)w1;
+            }
         }
         s_scale[(2 * pair) * (C::GPC + 2) + g] = __float2half_rn(stored_scale<QMAX>(hi0 - lo0, sc0, d.by_div));
         s_scale[(2 * pair + 1) * (C::GPC + 2) + g] = __float2half_rn(stored_scale<QMAX>(hi1 - lo1, sc1, d.by_div));
@@ -283,9 +295,14 @@ static int launch_bits(const kvq_quant_args *a, const QuantDims &d, cudaStream_t
     if (a->x_sS == 1 && G % E == 0 && tpg <= 32 && (tpg & (tpg - 1)) == 0) {
         bool vec_ok = sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && d.x_sB % 8 == 0 &&
                       d.x_sH % 8 == 0 && d.x_sA % 8 == 0;
-        const int64_t blocks = (total_words + 255) / 256;
-        quant_contig_kernel<BITS, T><<<(unsigned)blocks, 256, 0, st>>>(x, a->code, sc, mn, d, tpg, vec_ok);
-        return check_launch();
+        const int64_t per_slab = d.A * (d.S / E);
+        if (per_slab < (1LL << 31) && d.B * d.H <= 65535) {
+            const int64_t wpr = d.S / E;
+            const bool linear = d.x_sA == d.S && d.c_sA == wpr && d.z_sA == wpr / tpg;
+            dim3 grid((unsigned)((per_slab + 255) / 256), (unsigned)(d.B * d.H));
+            quant_contig_kernel<BITS, T><<<grid, 256, 0, st>>>(x, a->code, sc, mn, d, tpg, vec_ok, linear);
+            return check_launch();
+        }
     }
     // groups along a strided axis, channels contiguous (keys in [T, D] order)
     if constexpr (sizeof(T) == 2) {
