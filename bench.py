@@ -131,7 +131,7 @@ def run_reference(args, cfg):
     if rank != 0:
         return
     base = cpu_baseline(cfg, budget_s=30.0, steps=max(1, args.steps) if args.steps_given else None)
-    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+    line = {"impl": "reference", "metric": METRIC if args.config == 2 else f"decode tokens/s, KV-cache hot path, {cfg.name}", "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step_full_batch"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 data, f32 accumulate, u32 packed codes", "data": "synthetic",
@@ -153,6 +153,9 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="override the global batch (smaller smoke runs)")
     ap.add_argument("--context", type=int, default=None, help="override the context length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 5],
+                    help="2: Llama-2-7B b64 ctx4k (the headline, batch-sharded); 3: Mistral-7B GQA b8 ctx32k (batch-sharded); "
+                         "5: Llama-3-8B b1 ctx131k (KV heads sharded, per-layer NCCL all-gather of the attention output)")
     args = ap.parse_args()
     args.steps_given = args.steps is not None
     if args.steps is None:
@@ -160,7 +163,7 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
 
     from kvmix_b200 import configs
-    cfg = configs.config2()
+    cfg = {2: configs.config2, 3: configs.config3, 5: configs.config5}[args.config]()
     if args.batch:
         cfg.batch = args.batch
     if args.context:
@@ -183,12 +186,17 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     from kvmix_b200 import sharding
-    b_lo, b_hi = sharding.shard_batch(cfg.batch, world, rank)   # strong scaling: the global batch is split
-    B = b_hi - b_lo
     W, K = args.warmup, args.steps
-    L, nh, hkv, D = cfg.n_layers, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+    L, D = cfg.n_layers, cfg.head_dim
+    head_sharded = cfg.shard == "kv_head" and world > 1
+    if head_sharded:                                            # every rank holds all sequences, some KV heads
+        (k_lo, k_hi), (q_lo, q_hi) = sharding.shard_kv_heads(cfg.n_heads, cfg.n_kv_heads, world, rank)
+        B, nh, hkv = cfg.batch, q_hi - q_lo, k_hi - k_lo
+    else:                                                       # strong scaling: the global batch is split
+        b_lo, b_hi = sharding.shard_batch(cfg.batch, world, rank)
+        B, nh, hkv = b_hi - b_lo, cfg.n_heads, cfg.n_kv_heads
 
-    caches = configs.build_layer_caches(cfg, B, dev, extra_tokens=2 * (W + K) + 8, seed=rank)
+    caches = configs.build_layer_caches(cfg, B, dev, extra_tokens=2 * (W + K) + 8, kv_heads=hkv, seed=rank)
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     mk = lambda h: torch.randn((B, h, 1, D), generator=g, device=dev, dtype=torch.float16)
     dq, dk, dv = [mk(nh) for _ in range(L)], [mk(hkv) for _ in range(L)], [mk(hkv) for _ in range(L)]
@@ -212,7 +220,10 @@ def main():
                 attn_events.append((e0, e1, c.packed_bytes() + 2 * B * nh * D * 2))
             else:
                 c.attend(dq[l], out=dout[l])
+            if head_sharded:                                    # the one exchange step of the path (NCCL over NVLink)
+                gathered[l] = sharding.all_gather_heads(dout[l])
 
+    gathered = [None] * L
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(L)]
     ev_done = [torch.cuda.Event() for _ in range(L)]
@@ -232,6 +243,8 @@ def main():
         for l in range(L):
             cur.wait_event(ev_in[l])
             caches[l].decode_step(dq[l], dk[l], dv[l], out=dout[l])
+            if head_sharded:
+                gathered[l] = sharding.all_gather_heads(dout[l])
             ev_done[l].record(cur)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_done[l])
@@ -290,21 +303,26 @@ def main():
         peak, peak_src = measured_peak_gbs()
         achieved = attn_bytes_all / (attn_ms_all * 1e-3) / 1e9
         line = {
-            "metric": METRIC, "value": cfg.batch * K / (ms_total * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "metric": METRIC if args.config == 2 else f"decode tokens/s, KV-cache hot path, {cfg.name}",
+            "value": cfg.batch * K / (ms_total * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16 data, f32 accumulate, u32 packed codes", "data": "synthetic",
             "config": {"workload": cfg.name, "global_batch": cfg.batch, "batch_per_gpu": B, "context": cfg.context,
                        "context_at_end": ctx_now, "layers": L, "heads": nh, "kv_heads": hkv, "head_dim": D,
                        "group": cfg.group_size, "fp16_window": cfg.residual_length,
-                       "bit_map": "8xK4V4 + 12xK3V2(g11) + 12xK2V2, seeded shuffle",
+                       "bit_map": ", ".join(f"{n}xK{kb}V{vb}" for (kb, vb), n in sorted(
+                           {(q["k_bits"], q["v_bits"]): sum(1 for r in cfg.quant_bits.values()
+                                                            if (r["k_bits"], r["v_bits"]) == (q["k_bits"], q["v_bits"]))
+                            for q in cfg.quant_bits.values()}.items(), reverse=True)) + " (3-bit keys use group 11), seeded",
                        "l2_policy": "inputs larger than L2: every step streams the whole cache "
                                     f"({attn_bytes_all / max(1, n_attn) * L / 1e9:.1f} GB per step per GPU)",
-                       "parallelism": f"batch-sharded x{world}, no data-path collective"},
+                       "parallelism": (f"kv-head-sharded x{world}, per-layer NCCL all-gather of the attention output"
+                                       if head_sharded else f"batch-sharded x{world}, no data-path collective")},
             "roofline": {"bound": "hbm", "kernel": "decode_attn_mma_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "peak_source": peak_src,
-                         "traffic": (sum(NCU_TRAFFIC_PER_UNIT.get((q["k_bits"], q["v_bits"]), float("nan"))
-                                         for q in cfg.quant_bits.values()) / L * B * nh),
+                         "traffic": (sum(NCU_TRAFFIC_PER_UNIT[(q["k_bits"], q["v_bits"])]
+                                         for q in cfg.quant_bits.values()) / L * B * nh) if args.config == 2 else None,
                          "traffic_note": "bytes per launch (layer average), ncu dram read+write of a B=16 capture scaled by units",
                          "bytes_per_launch": attn_bytes_all / max(1, n_attn),
                          "us_per_launch": attn_ms_all * 1e3 / max(1, n_attn), "launches_timed": n_attn,

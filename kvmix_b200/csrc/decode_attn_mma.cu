@@ -1,4 +1,4 @@
-// Fused decode attention, tensor-core path (multi-head attention: one query head per kv head).
+// Fused decode attention, tensor-core path (one CTA per query head and token split; grouped queries share L2).
 //
 // Why tensor cores for a mat-vec: at the HBM rate a B200 has only ~1-3 issue slots per packed code
 // (2.8 per 2-bit code at 5.6 TB/s and 1.9 GHz).  Shift-mask-convert-FMA per code does not fit; one
@@ -110,6 +110,57 @@ template <> struct Fields<3> {
     }
 };
 
+// Value-side field extraction: same contract as Fields, but every field is moved to bit position >= 4 (>= 2
+// for 4-bit codes) of its 16-bit half.  The tensor core aligns the 16 products of an MMA (and the accumulator) to
+// the largest operand EXPONENT and truncates what falls about 26 bits below it; a subnormal's exponent is fixed at
+// -14 however small its value, so a code parked in the lowest mantissa bits loses low product bits whenever a
+// neighbouring token's probability is larger.  The loss is always downwards, so over a long, diffuse softmax it
+// adds up to a bias (2e-5 of the non-negative code sum for 2-bit codes at position 0, a quarter of that per two
+// positions higher) which the centring of the codes amplifies.  Two more shifts per word pair keep it below the
+// fp32 accumulation error.
+template <int BITS> struct VFields;
+
+template <> struct VFields<4> {
+    static constexpr int N = 8;
+    __device__ static __forceinline__ int pos(int i) { return (i & 1) ? 6 : 2; }
+    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[8]) {
+        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
+        const uint32_t lou = lo << 2, lod = lo >> 6, hiu = hi << 2, hid = hi >> 6;
+        r[0] = lou & 0x003c003cu; r[1] = lou & 0x03c003c0u; r[2] = lod & 0x003c003cu; r[3] = lod & 0x03c003c0u;
+        r[4] = hiu & 0x003c003cu; r[5] = hiu & 0x03c003c0u; r[6] = hid & 0x003c003cu; r[7] = hid & 0x03c003c0u;
+    }
+};
+
+template <> struct VFields<2> {
+    static constexpr int N = 16;
+    __device__ static __forceinline__ int pos(int i) { const int t = i & 7; return t < 2 ? 6 + 2 * t : t < 5 ? 2 * t : 2 * t - 6; }
+    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[16]) {
+        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
+        const uint32_t lou = lo << 6, lod = lo >> 6, hiu = hi << 6, hid = hi >> 6;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) { r[t] = lou & (0x00030003u << (6 + 2 * t)); r[8 + t] = hiu & (0x00030003u << (6 + 2 * t)); }
+#pragma unroll
+        for (int t = 2; t < 5; ++t) { r[t] = lo & (0x00030003u << (2 * t)); r[8 + t] = hi & (0x00030003u << (2 * t)); }
+#pragma unroll
+        for (int t = 5; t < 8; ++t) { r[t] = lod & (0x00030003u << (2 * t - 6)); r[8 + t] = hid & (0x00030003u << (2 * t - 6)); }
+    }
+};
+
+template <> struct VFields<1> {
+    static constexpr int N = 32;
+    __device__ static __forceinline__ int pos(int i) { const int t = i & 15; return t < 4 ? t + 6 : t < 10 ? t : t - 6; }
+    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[32]) {
+        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
+        const uint32_t lou = lo << 6, lod = lo >> 6, hiu = hi << 6, hid = hi >> 6;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) { r[t] = lou & (0x00010001u << (t + 6)); r[16 + t] = hiu & (0x00010001u << (t + 6)); }
+#pragma unroll
+        for (int t = 4; t < 10; ++t) { r[t] = lo & (0x00010001u << t); r[16 + t] = hi & (0x00010001u << t); }
+#pragma unroll
+        for (int t = 10; t < 16; ++t) { r[t] = lod & (0x00010001u << (t - 6)); r[16 + t] = hid & (0x00010001u << (t - 6)); }
+    }
+};
+
 // ---------------------------------------------------------------------------------------------
 // Key-side geometry per bit width.  A warp tile is 8 lane-octets x TPO tokens; code words reach the
 // warp through its own ring of cp.async stages in shared memory (padded rows so the fragment loads
@@ -179,6 +230,12 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     uint16_t v;
     asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
     return v;
+}
+// {lo, hi} -> fp16x2, round to nearest, saturating to the largest finite fp16 instead of overflowing to inf
+__device__ __forceinline__ uint32_t pack_h2_sat(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
 }
 __device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 __device__ __forceinline__ __half2 as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
@@ -408,7 +465,7 @@ template <int VB, int MODE>
 __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int32_t *vc, const __half *vs,
                                               const __half *vz, const MmaSmem &sm, int t0, int hi) {
     using G = VGeom<VB>;
-    using F = Fields<VB>;
+    using F = VFields<VB>;
     constexpr int WPO = (VB == 4) ? 2 : 1;                    // words per octet (16 channels)
     constexpr int NF = (VB == 1) ? 16 : F::N;                 // fields used per word (1-bit: one 16-bit half)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
@@ -476,6 +533,26 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
 #pragma unroll
     for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
     const uint32_t ones = 0x3c003c00u;
+    // The MMA accumulators hold sums of non-negative terms (codes and p are >= 0) whose centred difference is
+    // the result, and the tensor core adds into its fp32 accumulator with truncation: measured on a chain of
+    // 128 MMAs the sum comes out 1.7e-6 low (1e-7 after 32, exact to 2e-8 when restarted every 16), which the
+    // cancellation multiplies by a few hundred at 131k diffuse tokens.  Chains are therefore kept short: every
+    // kFlush stages the columns this lane owns are added to fp32 sums (round to nearest) and restart from zero.
+    constexpr int kFlush = 16;
+    float sum[8][2], sumz[2] = {0.f, 0.f};
+#pragma unroll
+    for (int m = 0; m < 8; ++m) sum[m][0] = sum[m][1] = 0.f;
+    auto flush = [&]() {
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            sum[m][0] += acc[m][0];
+            sum[m][1] += acc[m][2];
+            acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+        }
+        sumz[0] += accz[0];
+        sumz[1] += accz[1];
+        accz[0] = accz[1] = accz[2] = accz[3] = 0.f;
+    };
 
     if (MODE != 2) {
 #pragma unroll
@@ -496,7 +573,9 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
         __syncwarp();
         // ---- B operands for the stage: 16 token pairs x 8 columns -----------------------------------
         {
-            const float p0 = pp[bt0], p1 = pp[bt1];
+            // p is scaled by 2^8 before the fp16 rounding so that the many small probabilities of a long, diffuse
+            // context stay in the normal fp16 range (p <= 1, so this saturates only if a scale exceeds 255)
+            const float p0 = pp[bt0] * 256.f, p1 = pp[bt1] * 256.f;
             const float s00 = __half2float(__ushort_as_half((unsigned short)lds16(o00 + st)));
             const float s01 = __half2float(__ushort_as_half((unsigned short)lds16(o01 + st)));
             const float s10 = __half2float(__ushort_as_half((unsigned short)lds16(o10 + st)));
@@ -507,10 +586,10 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
             const float z11 = __half2float(__ushort_as_half((unsigned short)lds16(o11 + st + 256)));
             // columns 4ch .. 4ch+3 = (p*scale_g0, p*mid_g0, p*scale_g1, p*mid_g1), each a half2 over the token pair;
             // mid = zero + MID*scale is the midpoint of the group: codes are used as (code - MID)
-            const uint32_t c0 = as_u32(__floats2half2_rn(p0 * s00, p1 * s10));
-            const uint32_t c1 = as_u32(__floats2half2_rn(p0 * fmaf(G::MID, s00, z00), p1 * fmaf(G::MID, s10, z10)));
-            const uint32_t c2 = as_u32(__floats2half2_rn(p0 * s01, p1 * s11));
-            const uint32_t c3 = as_u32(__floats2half2_rn(p0 * fmaf(G::MID, s01, z01), p1 * fmaf(G::MID, s11, z11)));
+            const uint32_t c0 = pack_h2_sat(p0 * s00, p1 * s10);
+            const uint32_t c1 = pack_h2_sat(p0 * fmaf(G::MID, s00, z00), p1 * fmaf(G::MID, s10, z10));
+            const uint32_t c2 = pack_h2_sat(p0 * s01, p1 * s11);
+            const uint32_t c3 = pack_h2_sat(p0 * fmaf(G::MID, s01, z01), p1 * fmaf(G::MID, s11, z11));
             asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(pb_wr), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
         }
         __syncwarp();
@@ -545,20 +624,22 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
         st = (st + G::STAGE_BYTES == G::NS * G::STAGE_BYTES) ? 0u : st + G::STAGE_BYTES;
         issue_st = (issue_st + G::STAGE_BYTES == G::NS * G::STAGE_BYTES) ? 0u : issue_st + G::STAGE_BYTES;
         pp += block_stride;
+        if ((q % kFlush) == kFlush - 1) flush();
     }
+    flush();
     cp_async_wait<0>();
     __syncwarp();
     // epilogue: channel c = 16 g + i (i = 2m + r); columns 2*grp (sum p*scale) and 2*grp+1 (sum p*mid) sit in tig == grp
     if (tig == grp) {
         float *red = my_red + 16 * g;
-        const float corr = accz[1] - G::MID * accz[0];
+        const float corr = (sumz[1] - G::MID * sumz[0]) * (1.f / 256.f);          // undo the 2^8 carried by the B operands
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 const int i = 2 * m + r;
                 const int fi = i % NF;
-                red[i] = fmaf(acc[m][2 * r], (float)(1 << (24 - F::pos(fi))), corr);
+                red[i] = fmaf(sum[m][r], (float)(1 << (16 - F::pos(fi))), corr);
             }
         }
     }
@@ -622,8 +703,11 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
     sm.misc = reinterpret_cast<float *>(sm.q + kHeadDim);
 
     const int split = blockIdx.x % n_splits;
-    const int s = blockIdx.x / n_splits;                      // b * nh + h  (nh == nh_kv on this path)
+    const int s = blockIdx.x / n_splits;                      // b * nh + h
     const int b = s / a.nh, h = s % a.nh;
+    // grouped queries: each query head is its own CTA and reads kv head hk; the heads of one kv head are
+    // neighbouring CTAs, so the cache is fetched from HBM once and re-read from L2
+    const int hk = h / (a.nh / a.nh_kv);
     const int t0 = split * chunk, t1 = min(a.T, t0 + chunk);
 
     const __half *q = static_cast<const __half *>(a.q) + (int64_t)b * a.q_sB + (int64_t)h * a.q_sH;
@@ -635,19 +719,19 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
     {
         const int hi = min(t1, a.Tkq);
         if (t0 < hi) {
-            const int32_t *kc = a.kcode + (int64_t)b * a.kc_sB + (int64_t)h * a.kc_sH;
-            const __half *ks = static_cast<const __half *>(a.kscale) + (int64_t)b * a.ks_sB + (int64_t)h * a.ks_sH;
-            const __half *kz = static_cast<const __half *>(a.kmn) + (int64_t)b * a.ks_sB + (int64_t)h * a.ks_sH;
-            const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)h * a.kf_sH;
+            const int32_t *kc = a.kcode + (int64_t)b * a.kc_sB + (int64_t)hk * a.kc_sH;
+            const __half *ks = static_cast<const __half *>(a.kscale) + (int64_t)b * a.ks_sB + (int64_t)hk * a.ks_sH;
+            const __half *kz = static_cast<const __half *>(a.kmn) + (int64_t)b * a.ks_sB + (int64_t)hk * a.ks_sH;
+            const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)hk * a.kf_sH;
             qk_packed_mma<KB>(a, kc, ks, kz, sm, t0, hi, kf, max(t0, a.Tkq), t1);
         } else if (t0 < t1) {
-            const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)h * a.kf_sH;
+            const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)hk * a.kf_sH;
             qk_tail_mma(a, kf, sm, t0, t0, t1);
         }
     }
-    const int32_t *vc = a.vcode + (int64_t)b * a.vc_sB + (int64_t)h * a.vc_sH;
-    const __half *vs = static_cast<const __half *>(a.vscale) + (int64_t)b * a.vs_sB + (int64_t)h * a.vs_sH;
-    const __half *vz = static_cast<const __half *>(a.vmn) + (int64_t)b * a.vs_sB + (int64_t)h * a.vs_sH;
+    const int32_t *vc = a.vcode + (int64_t)b * a.vc_sB + (int64_t)hk * a.vc_sH;
+    const __half *vs = static_cast<const __half *>(a.vscale) + (int64_t)b * a.vs_sB + (int64_t)hk * a.vs_sH;
+    const __half *vz = static_cast<const __half *>(a.vmn) + (int64_t)b * a.vs_sB + (int64_t)hk * a.vs_sH;
     const int v_hi = min(t1, a.Tvq);
     if (t0 < v_hi) pv_packed_mma<VB, 1>(a, vc, vs, vz, sm, t0, v_hi);   // start filling this warp's value ring now
     __syncthreads();
@@ -676,7 +760,7 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
         if (t0 < v_hi) pv_packed_mma<VB, 2>(a, vc, vs, vz, sm, t0, v_hi);
         const int lo = max(t0, a.Tvq);
         if (lo < t1) {
-            const __half *vf = static_cast<const __half *>(a.vfull) + (int64_t)b * a.vf_sB + (int64_t)h * a.vf_sH;
+            const __half *vf = static_cast<const __half *>(a.vfull) + (int64_t)b * a.vf_sB + (int64_t)hk * a.vf_sH;
             const int co = tid & 15, tl = tid >> 4;           // 8 channels per thread, 8 token lanes per CTA
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int t = lo + tl; t < t1; t += 8) {
@@ -741,7 +825,7 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
 // The tensor-core path needs one query head per kv head, supported group sizes, 16-byte aligned and
 // row-contiguous packed tensors (cp.async granules), and a packed-value length that is a multiple of 16.
 bool mma_path_eligible(const kvq_attn_args &a) {
-    if (a.nh != a.nh_kv || a.D != kHeadDim) return false;
+    if (a.nh_kv <= 0 || a.nh % a.nh_kv != 0 || a.D != kHeadDim) return false;
     if (a.k_bits == 3) {
         if (a.k_group != 11) return false;
     } else if (a.k_group != 32 && a.k_group != 64 && a.k_group != 128) {
