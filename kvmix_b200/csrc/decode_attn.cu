@@ -24,16 +24,14 @@ struct SplitPlan {
     int chunk, n_splits;
 };
 
-// Splits start on a packed-word and key-group boundary: multiples of 128 tokens, or of 352 = 11*32
-// for 3-bit keys (11 tokens per word).
-static SplitPlan plan_splits(int T, int k_bits, int64_t heads, bool mma_path = false) {
-    // the tensor-core kernel iterates 1024 tokens (352 for 3-bit keys) per CTA step and holds up to 8192 scores
-    const int unit = (k_bits == 3) ? 352 : (mma_path ? 1024 : 128);
-    const int kMaxChunk = mma_path ? ((k_bits == 3) ? 8096 : 8192) : kvq::kMaxChunk;
+// Generic kernel: splits start on a packed-word and key-group boundary: multiples of 128 tokens, or of
+// 352 = 11*32 for 3-bit keys (11 tokens per word).
+static SplitPlan plan_splits_generic(int T, int k_bits, int64_t heads) {
+    const int unit = (k_bits == 3) ? 352 : 128;
     const int64_t want_ctas = 148 * 4;
     int64_t n = (T + kMaxChunk - 1) / kMaxChunk;
     const int64_t by_fill = (want_ctas + heads - 1) / heads;
-    const int64_t by_len = mma_path ? (T + 2047) / 2048 : (T + 4 * unit - 1) / (4 * unit);  // keep splits long
+    const int64_t by_len = (T + 4 * unit - 1) / (4 * unit);   // keep splits long
     n = n > (by_fill < by_len ? by_fill : by_len) ? n : (by_fill < by_len ? by_fill : by_len);
     if (n < 1) n = 1;
     int chunk = (int)((T + n - 1) / n);
@@ -43,6 +41,73 @@ static SplitPlan plan_splits(int T, int k_bits, int64_t heads, bool mma_path = f
     p.chunk = chunk;
     p.n_splits = (T + chunk - 1) / chunk;
     return p;
+}
+
+// Tensor-core kernel: a CTA step is 4 warps x one 256-token key tile (88 tokens for 3-bit keys), so chunks are
+// multiples of 1024 (352) tokens, at most 8192 (8096) scores are held, and the last split runs to T, absorbing a
+// remainder of up to a quarter step.  The chunk is the candidate with the best estimated throughput under a
+// model fitted to measurements on B200 (2-bit keys and values, 256..8192 CTAs of 1024..8192 tokens):
+//   rate ~ q / ceil(q) * chunk / (chunk + 670),  q = CTAs / (148 SMs * 3 resident CTAs),
+// i.e. whole waves of CTAs and a fixed cost per CTA worth 670 tokens (7 us against 10.5 us per 1000 tokens); chunks
+// under 4096 tokens measured a further ~10 % below that and more than one split pays for the counter reset and the
+// merge.  Ties go to fewer splits.
+constexpr int kMmaSlots = 148 * 3;
+constexpr double kMmaCtaCost = 670.0;
+
+struct PlanMemo {
+    int T, kb;
+    int64_t heads;
+    SplitPlan plan;
+};
+
+static SplitPlan plan_splits_mma(int T, int k_bits, int64_t heads) {
+    const int unit = (k_bits == 3) ? 352 : 1024;
+    const int max_chunk = (k_bits == 3) ? 8096 : 8192;
+    static thread_local PlanMemo memo[4] = {};
+    static thread_local int next = 0;
+    for (const PlanMemo &m : memo)
+        if (m.T == T && m.kb == k_bits && m.heads == heads) return m.plan;
+
+    // no finer than ~16 CTAs per slot in total: bounds the search and the workspace
+    const int64_t n_cap = (16 * kMmaSlots + heads - 1) / heads;
+    SplitPlan best = {0, 0};
+    double best_rate = 0.0;
+    for (int chunk = (max_chunk / unit) * unit; chunk >= unit; chunk -= unit) {
+        int n = (T + chunk - 1) / chunk;
+        int last = T - (n - 1) * chunk;
+        if (n > 1 && last <= unit / 4) {
+            --n;
+            last += chunk;
+        }
+        if (n > n_cap && best.n_splits > 0) break;
+        const double q = (double)(heads * n) / kMmaSlots;
+        const double waves = (double)((heads * n + kMmaSlots - 1) / kMmaSlots);
+        const double longest = chunk > last ? chunk : last;
+        double rate = q / waves * ((double)T / n) / (longest + kMmaCtaCost);
+        if (longest < 4096) rate *= 0.9;
+        if (n > 1) rate *= 0.97;
+        if (rate > best_rate * 1.0001) {
+            best = {chunk, n};
+            best_rate = rate;
+        }
+    }
+    memo[next] = {T, k_bits, heads, best};
+    next = (next + 1) & 3;
+    return best;
+}
+
+// Upper bound of plan_splits_mma's split count for every T' <= T (the workspace is sized once for a cache).
+static int64_t max_splits_mma(int T, int k_bits, int64_t heads) {
+    const int unit = (k_bits == 3) ? 352 : 1024;
+    const int max_chunk = (k_bits == 3) ? 8096 : 8192;
+    const int64_t n_cap = (16 * kMmaSlots + heads - 1) / heads;
+    const int64_t by_unit = (T + unit - 1) / unit, by_max = (T + (max_chunk / unit) * unit - 1) / ((max_chunk / unit) * unit);
+    const int64_t n = by_unit < n_cap ? by_unit : n_cap;
+    return n > by_max ? n : by_max;
+}
+
+static SplitPlan plan_splits(int T, int k_bits, int64_t heads, bool mma_path = false) {
+    return mma_path ? plan_splits_mma(T, k_bits, heads) : plan_splits_generic(T, k_bits, heads);
 }
 
 struct Smem {
@@ -273,11 +338,11 @@ extern "C" uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32
     if (B <= 0 || nh <= 0 || T <= 0) return 256;
     const int64_t heads = (int64_t)B * nh;
     int64_t ns = 1;
-    for (int kb = 3; kb <= 4; ++kb)
-        for (int mma = 0; mma < 2; ++mma) {
-            const SplitPlan p = plan_splits(T, kb, heads, mma != 0);
-            if (p.n_splits > ns) ns = p.n_splits;
-        }
+    for (int kb = 3; kb <= 4; ++kb) {
+        const int64_t g = plan_splits_generic(T, kb, heads).n_splits, m = max_splits_mma(T, kb, heads);
+        ns = g > ns ? g : ns;
+        ns = m > ns ? m : ns;
+    }
     uint64_t bytes = (uint64_t)heads * 4;
     bytes = (bytes + 255) / 256 * 256;
     bytes += (uint64_t)heads * ns * kPartStride * 4;

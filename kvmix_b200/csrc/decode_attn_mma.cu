@@ -29,8 +29,7 @@ constexpr int kMmaWarps = 4;
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -240,6 +239,20 @@ __device__ __forceinline__ uint32_t pack_h2_sat(float lo, float hi) {
 __device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 __device__ __forceinline__ __half2 as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 
+// Optional phase clock (build with -DKVQ_PHASE_TIMING): thread 0 of the first 4096 CTAs stamps %globaltimer at
+// the phase boundaries; kvq_debug_phases() copies the stamps out.  0 start, 1 q stored, 2 scores done, 3 softmax
+// done, 4 fp16 value tail done, 5 packed values done.
+#ifdef KVQ_PHASE_TIMING
+__device__ unsigned long long g_phase[4096 * 8];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define PHASE(i) do { if (threadIdx.x == 0 && blockIdx.x < 4096) g_phase[blockIdx.x * 8 + (i)] = gtime(); } while (0)
+#else
+#define PHASE(i)
+#endif
 struct MmaSmem {
     float *scores;          // [n_scores]
     unsigned char *ring;    // this warp's region
@@ -269,6 +282,7 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     const int n_tiles = (hi - t0 + G::WT - 1) / G::WT;
     const int my_tiles = (n_tiles - warp + kMmaWarps - 1) / kMmaWarps;   // tiles warp, warp+4, ...
     if (my_tiles <= 0) {
+        __syncthreads();                                       // q is in shared memory (see below)
         if (tail_lo < t1) qk_tail_mma(a, kf, sm, t0, tail_lo, t1);
         return;
     }
@@ -279,9 +293,13 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     const uint32_t sz_s = ring_s + G::NS * G::STAGE_BYTES;                    // [2][128][8] halfs
     const int gr = lane % G::GPR, row0 = lane / G::GPR;
     const uint32_t cp_dst = ring_s + row0 * G::RS + gr * 16;                   // + slot*STAGE + i*RPI*RS
-    const uint32_t frag_s = ring_s + (2 * tig) * G::RS + g * (4 * G::WPL);     // + slot*STAGE + (16k + rr)*RS
-    const int gw = (g * G::TPO) / Gk;                                          // group of this octet inside the warp tile
-    const uint32_t szl_s = sz_s + ((2 * tig) * 8 + gw) * 2;                    // + (16 ksx + {0,1,8,9}) * 16 [+ 2048 for zero]
+    // 3-bit: octet g owns the word of group g (11 tokens).  Other widths: the tile is worked as two halves of 128
+    // tokens, octet g owning tokens [128 h + 16 g, +16) of half h, so that the 16 rows of one MMA touch at most four
+    // groups and the eight B columns can carry {hi, lo} of q*scale for those four side by side.
+    constexpr int HW = (KB == 4) ? 2 : 1;                                      // code words per octet per half
+    const uint32_t frag_s = (KB == 3) ? ring_s + (2 * tig) * G::RS + g * 4
+                                      : ring_s + (2 * tig) * G::RS + ((KB == 4) ? 8 * g : (KB == 2) ? 4 * g : 4 * (g >> 1));
+    const int wshift = (KB == 1) ? 16 * (g & 1) : 0;
     // ldmatrix.x4 row addresses: lanes 0-7 scale rows 16ksx+0..7, 8-15 scale rows +8..15, 16-31 the same of the zero tile
     const uint32_t ldm_s = sz_s + (((lane >> 3) & 1) * 8 + (lane & 7)) * 16 + (lane >> 4) * 2048;
     const uint32_t q_s = smem_u32(sm.q) + (2 * tig) * 2;                       // + 32 ksx [+16]
@@ -321,13 +339,14 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     cp_async_commit();
     issue_stage(tb_cur, ok_cur, 2);
     cp_async_commit();
+    // The caller stored q to shared memory just before this call without a barrier, so that the first code stages
+    // are in flight while q arrives; every warp passes exactly one barrier here before anything reads q.
+    __syncthreads();
     if (tail_lo < t1) qk_tail_mma(a, kf, sm, t0, tail_lo, t1);
 
     const uint32_t ones = 0x3c003c00u;
     for (int j = 0; j < my_tiles; ++j) {
         const int tile0 = t0 + (j * kMmaWarps + warp) * G::WT;
-        const int tok0 = tile0 + g * G::TPO;                   // first token of this octet's chunk
-        const bool live = tok0 < hi;                           // chunks are whole or absent (hi is a group multiple)
         const bool have_next = j + 1 < my_tiles;
         const int32_t *tb_nxt = tb_cur + tile_words;
         const bool ok_nxt = have_next && (wcol_cur + tile_words < n_words);
@@ -336,39 +355,52 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
         cp_async_wait<2>();
         __syncwarp();
         // ---- B fragments q*scale and the zero term sum_d q[d]*zero[d,g] ----------------------------------
-        // q*scale needs 22 bits; it is carried as an fp16 pair hi + lo (lo = fma(q, s, -hi) is exact) and every
-        // code tile is multiplied by both, so the key side adds no rounding beyond the fp32 accumulation.  The
-        // zero term gets the same treatment and is summed over channels by an MMA whose A operand is all ones.
-        uint32_t bq[8][2], bl[8][2];
-        float accz[4] = {0.f, 0.f, 0.f, 0.f};
+        // q*scale needs 22 bits; it is carried as an fp16 pair hi + lo (lo = fma(q, s, -hi) is exact), so the key
+        // side adds no rounding beyond the fp32 accumulation.  The zero term gets the same treatment and is summed
+        // over channels by MMAs whose A operand is all ones (one accumulator per half of the pair: short chains).
+        // 3-bit keys: b0 = hi and b1 = lo of the eight groups of the tile, every code tile is multiplied by both.
+        // Other widths: b0 / b1 serve the first / second half of the tile; column n carries group (n / 2) of that
+        // half, hi in even and lo in odd columns, so one MMA per code tile yields both parts.
+        uint32_t b0[8][2], b1[8][2];
+        float accz[4] = {0.f, 0.f, 0.f, 0.f}, accy[4] = {0.f, 0.f, 0.f, 0.f};
+        const int gph = ngw > 1 ? ngw / 2 : 1;                 // groups per half tile: 4 / 2 / 1
+        const int src0 = 4 * ((g >> 1) % gph) + tig;           // lane holding group (n / 2) of the first half
+        const int src1 = src0 + 4 * (ngw / 2);
+        const bool odd = g & 1;
 #pragma unroll
         for (int ksx = 0; ksx < 8; ++ksx) {
             const __half2 q01 = as_h2(lds32(q_s + 32 * ksx)), q89 = as_h2(lds32(q_s + 32 * ksx + 16));
-            __half2 s01, s89, z01, z89;
-            if (ngw == 8) {
-                // the tile rows are 8 groups x fp16 = one 8x8 matrix per 8 channels: a transposing ldmatrix hands
-                // lane (g, tig) exactly {row 2tig, row 2tig+1} x column g, i.e. its B-fragment pairs, in one go
-                uint32_t r0, r1, r2, r3;
-                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                             : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(ldm_s + ksx * 256));
-                s01 = as_h2(r0); s89 = as_h2(r1); z01 = as_h2(r2); z89 = as_h2(r3);
-            } else {
-                const uint32_t so = szl_s + ksx * 256;
-                s01 = as_h2(lds16(so) | (lds16(so + 16) << 16));
-                s89 = as_h2(lds16(so + 128) | (lds16(so + 144) << 16));
-                z01 = as_h2(lds16(so + 2048) | (lds16(so + 2064) << 16));
-                z89 = as_h2(lds16(so + 2176) | (lds16(so + 2192) << 16));
-            }
-            const __half2 b01 = __hmul2(q01, s01), b89 = __hmul2(q89, s89);
+            // the tile rows are 8 groups x fp16 = one 8x8 matrix per 8 channels: a transposing ldmatrix hands
+            // lane (g, tig) exactly {row 2tig, row 2tig+1} x column g, i.e. its B-fragment pairs of group g, in one go
+            // (with fewer than 8 groups per tile the columns past the last group are stale and feed unused columns)
+            uint32_t r0, r1, r2, r3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                         : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(ldm_s + ksx * 256));
+            const __half2 z01 = as_h2(r2), z89 = as_h2(r3);
             const __half2 y01 = __hmul2(q01, z01), y89 = __hmul2(q89, z89);
-            bq[ksx][0] = as_u32(b01);
-            bq[ksx][1] = as_u32(b89);
-            bl[ksx][0] = as_u32(__hfma2(q01, s01, __hneg2(b01)));
-            bl[ksx][1] = as_u32(__hfma2(q89, s89, __hneg2(b89)));
             mma16816(accz, ones, ones, ones, ones, as_u32(y01), as_u32(y89));
-            mma16816(accz, ones, ones, ones, ones, as_u32(__hfma2(q01, z01, __hneg2(y01))), as_u32(__hfma2(q89, z89, __hneg2(y89))));
+            mma16816(accy, ones, ones, ones, ones, as_u32(__hfma2(q01, z01, __hneg2(y01))), as_u32(__hfma2(q89, z89, __hneg2(y89))));
+            if constexpr (KB == 3) {
+                const __half2 s01 = as_h2(r0), s89 = as_h2(r1);
+                const __half2 p01 = __hmul2(q01, s01), p89 = __hmul2(q89, s89);
+                b0[ksx][0] = as_u32(p01);
+                b0[ksx][1] = as_u32(p89);
+                b1[ksx][0] = as_u32(__hfma2(q01, s01, __hneg2(p01)));
+                b1[ksx][1] = as_u32(__hfma2(q89, s89, __hneg2(p89)));
+            } else {
+                const __half2 sa01 = as_h2(__shfl_sync(0xffffffffu, r0, src0)), sa89 = as_h2(__shfl_sync(0xffffffffu, r1, src0));
+                const __half2 sb01 = as_h2(__shfl_sync(0xffffffffu, r0, src1)), sb89 = as_h2(__shfl_sync(0xffffffffu, r1, src1));
+                const __half2 pa01 = __hmul2(q01, sa01), pa89 = __hmul2(q89, sa89);
+                const __half2 pb01 = __hmul2(q01, sb01), pb89 = __hmul2(q89, sb89);
+                b0[ksx][0] = odd ? as_u32(__hfma2(q01, sa01, __hneg2(pa01))) : as_u32(pa01);
+                b0[ksx][1] = odd ? as_u32(__hfma2(q89, sa89, __hneg2(pa89))) : as_u32(pa89);
+                b1[ksx][0] = odd ? as_u32(__hfma2(q01, sb01, __hneg2(pb01))) : as_u32(pb01);
+                b1[ksx][1] = odd ? as_u32(__hfma2(q89, sb89, __hneg2(pb89))) : as_u32(pb89);
+            }
         }
         __syncwarp();                                          // everyone has read the tile: it may be refilled
+#pragma unroll
+        for (int i = 0; i < 4; ++i) accz[i] += accy[i];
 
         float acc[G::NMMA][4];
 #pragma unroll
@@ -390,56 +422,103 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
 #pragma unroll
             for (int k = 0; k < G::KSPS; ++k) {
                 const int ksx = st * G::KSPS + k;
-                uint32_t w[4][G::WPL];
+                if constexpr (KB == 3) {
+                    uint32_t w[4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const uint32_t ad = src + (k * 16 + (r & 1) + (r >> 1) * 8) * G::RS;
-                    if constexpr (G::WPL == 4) {
-                        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
-                                     : "=r"(w[r][0]), "=r"(w[r][1]), "=r"(w[r][2]), "=r"(w[r][3]) : "r"(ad));
-                    } else if constexpr (G::WPL == 2) {
-                        asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];\n" : "=r"(w[r][0]), "=r"(w[r][1]) : "r"(ad));
-                    } else {
-                        w[r][0] = lds32(ad);
-                    }
-                }
-#pragma unroll
-                for (int x = 0; x < G::WPL; ++x) {
+                    for (int r = 0; r < 4; ++r) w[r] = lds32(src + (k * 16 + (r & 1) + (r >> 1) * 8) * G::RS);
                     uint32_t rlo[F::N], rhi[F::N];
-                    F::unpack(w[0][x], w[1][x], rlo);
-                    F::unpack(w[2][x], w[3][x], rhi);
+                    F::unpack(w[0], w[1], rlo);
+                    F::unpack(w[2], w[3], rhi);
 #pragma unroll
                     for (int i = 0; i < F::N; i += 2) {
-                        const int m = (x * F::N + i) / 2;
                         const uint32_t a1 = (i + 1 < F::N) ? rlo[i + 1] : 0u, a3 = (i + 1 < F::N) ? rhi[i + 1] : 0u;
-                        mma16816(acc[m], rlo[i], a1, rhi[i], a3, bq[ksx][0], bq[ksx][1]);
-                        mma16816(acc[m], rlo[i], a1, rhi[i], a3, bl[ksx][0], bl[ksx][1]);
+                        mma16816(acc[i / 2], rlo[i], a1, rhi[i], a3, b0[ksx][0], b0[ksx][1]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < F::N; i += 2) {
+                        const uint32_t a1 = (i + 1 < F::N) ? rlo[i + 1] : 0u, a3 = (i + 1 < F::N) ? rhi[i + 1] : 0u;
+                        mma16816(acc[i / 2], rlo[i], a1, rhi[i], a3, b1[ksx][0], b1[ksx][1]);
+                    }
+                } else {
+                    constexpr int NF = (KB == 1) ? 16 : F::N;              // fields used per word (1-bit: one 16-bit half)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t w[4][HW];
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) {
+                            const uint32_t ad = src + (k * 16 + (r & 1) + (r >> 1) * 8) * G::RS + h * (G::RB / 2);
+                            if constexpr (HW == 2) {
+                                asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];\n" : "=r"(w[r][0]), "=r"(w[r][1]) : "r"(ad));
+                            } else {
+                                w[r][0] = lds32(ad) >> wshift;
+                            }
+                        }
+#pragma unroll
+                        for (int x = 0; x < HW; ++x) {
+                            uint32_t rlo[F::N], rhi[F::N];
+                            F::unpack(w[0][x], w[1][x], rlo);
+                            F::unpack(w[2][x], w[3][x], rhi);
+#pragma unroll
+                            for (int i = 0; i < NF; i += 2) {
+                                const int m = h * 8 + (x * NF + i) / 2;
+                                if (h == 0) mma16816(acc[m], rlo[i], rlo[i + 1], rhi[i], rhi[i + 1], b0[ksx][0], b0[ksx][1]);
+                                else mma16816(acc[m], rlo[i], rlo[i + 1], rhi[i], rhi[i + 1], b1[ksx][0], b1[ksx][1]);
+                            }
+                        }
                     }
                 }
             }
             __syncwarp();                                      // slot st % NS is free for the stage NS ahead
         }
 
-        // ---- epilogue: the octet's column is n = g, held by the lane with tig == g/2 -----------------
-        if (live && tig == (g >> 1)) {
-            const bool sel = g & 1;
-            const float corr = sel ? accz[1] : accz[0];
-            float *dst = sm.scores + (tok0 - t0);
+        // ---- epilogue ----------------------------------------------------------------------------------
+        if constexpr (KB == 3) {
+            // the octet's column is n = g, held by the lane with tig == g/2
+            const int tok0 = tile0 + g * G::TPO;               // first token of this octet's chunk
+            if (tok0 < hi && tig == (g >> 1)) {                // chunks are whole or absent (hi is a group multiple)
+                const bool sel = g & 1;
+                const float corr = sel ? accz[1] : accz[0];
+                float *dst = sm.scores + (tok0 - t0);
 #pragma unroll
-            for (int m = 0; m < G::NMMA; ++m) {
-                const int i0 = 2 * m, i1 = 2 * m + 1;
-                float s0 = fmaf(sel ? acc[m][1] : acc[m][0], (float)(1 << (24 - F::pos(i0 % F::N))), corr);
-                float s1 = (i1 < G::TPO) ? fmaf(sel ? acc[m][3] : acc[m][2], (float)(1 << (24 - F::pos(i1 % F::N))), corr) : 0.f;
-                if (a.round_scores) {
-                    const float2 r = __half22float2(__floats2half2_rn(s0, s1));
-                    s0 = r.x;
-                    s1 = r.y;
-                }
-                if (i1 < G::TPO && (G::TPO % 2 == 0)) {
-                    *reinterpret_cast<float2 *>(dst + i0) = make_float2(s0 * a.softmax_scale, s1 * a.softmax_scale);
-                } else {
+                for (int m = 0; m < G::NMMA; ++m) {
+                    const int i0 = 2 * m, i1 = 2 * m + 1;
+                    float s0 = fmaf(sel ? acc[m][1] : acc[m][0], (float)(1 << (24 - F::pos(i0 % F::N))), corr);
+                    float s1 = (i1 < G::TPO) ? fmaf(sel ? acc[m][3] : acc[m][2], (float)(1 << (24 - F::pos(i1 % F::N))), corr) : 0.f;
+                    if (a.round_scores) {
+                        const float2 r = __half22float2(__floats2half2_rn(s0, s1));
+                        s0 = r.x;
+                        s1 = r.y;
+                    }
                     dst[i0] = s0 * a.softmax_scale;
                     if (i1 < G::TPO) dst[i1] = s1 * a.softmax_scale;
+                }
+            }
+        } else {
+            // octet g of half h is in group h*gph + cp of the tile, cp = 16 g / Gk; its hi and lo sums are the column
+            // pair cp, held by the lane with tig == cp; the group's zero term sits in another lane of the quad
+            constexpr int NF = (KB == 1) ? 16 : F::N;
+            const int cp = (16 * g) / Gk;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int grp = h * gph + cp;
+                const int zsrc = (lane & ~3) | ((grp >> 1) & 3);
+                const float z0 = __shfl_sync(0xffffffffu, accz[0], zsrc), z1 = __shfl_sync(0xffffffffu, accz[1], zsrc);
+                const float corr = (grp & 1) ? z1 : z0;
+                const int tok0 = tile0 + 128 * h + 16 * g;
+                if (tok0 < hi && tig == cp) {                  // 16-token chunks are whole or absent (hi is a group multiple)
+                    float *dst = sm.scores + (tok0 - t0);
+#pragma unroll
+                    for (int m = 0; m < 8; ++m) {
+                        const int i0 = (2 * m) % NF, i1 = (2 * m + 1) % NF;
+                        float s0 = fmaf(acc[h * 8 + m][0] + acc[h * 8 + m][1], (float)(1 << (24 - F::pos(i0))), corr);
+                        float s1 = fmaf(acc[h * 8 + m][2] + acc[h * 8 + m][3], (float)(1 << (24 - F::pos(i1))), corr);
+                        if (a.round_scores) {
+                            const float2 r = __half22float2(__floats2half2_rn(s0, s1));
+                            s0 = r.x;
+                            s1 = r.y;
+                        }
+                        *reinterpret_cast<float2 *>(dst + 2 * m) = make_float2(s0 * a.softmax_scale, s1 * a.softmax_scale);
+                    }
                 }
             }
         }
@@ -702,18 +781,22 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
     sm.q = reinterpret_cast<__half *>(sm.tailred + kMmaWarps * kHeadDim);
     sm.misc = reinterpret_cast<float *>(sm.q + kHeadDim);
 
-    const int split = blockIdx.x % n_splits;
-    const int s = blockIdx.x / n_splits;                      // b * nh + h
+    // split-major order: all heads' first splits, then their second ... ; the last split of a head is the short
+    // one (or absorbs a short remainder), so the grid's final wave is made of the cheapest CTAs
+    const int n_heads = a.B * a.nh;
+    const int split = blockIdx.x / n_heads;
+    const int s = blockIdx.x % n_heads;                       // b * nh + h
     const int b = s / a.nh, h = s % a.nh;
     // grouped queries: each query head is its own CTA and reads kv head hk; the heads of one kv head are
     // neighbouring CTAs, so the cache is fetched from HBM once and re-read from L2
     const int hk = h / (a.nh / a.nh_kv);
-    const int t0 = split * chunk, t1 = min(a.T, t0 + chunk);
+    const int t0 = split * chunk, t1 = (split == n_splits - 1) ? a.T : t0 + chunk;
 
+    PHASE(0);
     const __half *q = static_cast<const __half *>(a.q) + (int64_t)b * a.q_sB + (int64_t)h * a.q_sH;
     if (tid < kHeadDim) sm.q[tid] = q[tid];
     for (int i = tid; i < kMmaWarps * kHeadDim; i += kMmaThreads) sm.tailred[i] = 0.f;
-    __syncthreads();
+    PHASE(1);
 
     // ---- 1. scores ------------------------------------------------------------------------------
     {
@@ -724,9 +807,10 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
             const __half *kz = static_cast<const __half *>(a.kmn) + (int64_t)b * a.ks_sB + (int64_t)hk * a.ks_sH;
             const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)hk * a.kf_sH;
             qk_packed_mma<KB>(a, kc, ks, kz, sm, t0, hi, kf, max(t0, a.Tkq), t1);
-        } else if (t0 < t1) {
+        } else {
+            __syncthreads();                                   // q is in shared memory
             const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)hk * a.kf_sH;
-            qk_tail_mma(a, kf, sm, t0, t0, t1);
+            if (t0 < t1) qk_tail_mma(a, kf, sm, t0, t0, t1);
         }
     }
     const int32_t *vc = a.vcode + (int64_t)b * a.vc_sB + (int64_t)hk * a.vc_sH;
@@ -735,40 +819,73 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
     const int v_hi = min(t1, a.Tvq);
     if (t0 < v_hi) pv_packed_mma<VB, 1>(a, vc, vs, vz, sm, t0, v_hi);   // start filling this warp's value ring now
     __syncthreads();
+    PHASE(2);
 
     // ---- 2. softmax numerators ------------------------------------------------------------------
+    // The fp16 value tail of this split (the window: usually <= 128 tokens) is fetched into registers first, so its
+    // global-load latency is spent under the two softmax passes.  Thread (co, tl) owns 8 channels and tokens
+    // v_lo + tl + 8 j; rounds of 128 tokens, the first one preloaded.
     const int n = t1 - t0;
+    const int v_lo = max(t0, a.Tvq);
+    const __half *vf = static_cast<const __half *>(a.vfull) + (int64_t)b * a.vf_sB + (int64_t)hk * a.vf_sH;
+    const int co = tid & 15, tl = tid >> 4;
+    uint4 vt[16];
+    auto load_tail_round = [&](int base) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = base + tl + 8 * j;
+            int s0 = a.vf_start + (t - a.Tvq);
+            if (s0 >= a.vf_cap) s0 -= a.vf_cap;
+            vt[j] = (t < t1) ? __ldg(reinterpret_cast<const uint4 *>(vf + (int64_t)s0 * a.vf_sT) + co) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    if (v_lo < t1) load_tail_round(v_lo);
+
     float m = -3.0e38f;
-    for (int i = tid; i < n; i += kMmaThreads) m = fmaxf(m, sm.scores[i]);
+    const int n4 = (n + 3) >> 2;
+    float4 *sc4 = reinterpret_cast<float4 *>(sm.scores);
+#pragma unroll 4
+    for (int i = tid; i < n4; i += kMmaThreads) {
+        float4 v = sc4[i];
+        if (4 * i + 3 >= n) {                                  // the last, partial quad: neutral padding
+            if (4 * i + 1 >= n) v.y = -3.0e38f;
+            if (4 * i + 2 >= n) v.z = -3.0e38f;
+            v.w = -3.0e38f;
+            sc4[i] = v;
+        }
+        m = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+    }
     m = warp_max(m);
     if (lane == 0) sm.misc[warp] = m;
     __syncthreads();
     m = fmaxf(fmaxf(sm.misc[0], sm.misc[1]), fmaxf(sm.misc[2], sm.misc[3]));
     float l = 0.f;
-    for (int i = tid; i < n; i += kMmaThreads) {
-        const float p = __expf(sm.scores[i] - m);
-        sm.scores[i] = p;
-        l += p;
+#pragma unroll 4
+    for (int i = tid; i < n4; i += kMmaThreads) {
+        float4 v = sc4[i];
+        v.x = __expf(v.x - m);
+        v.y = __expf(v.y - m);
+        v.z = __expf(v.z - m);
+        v.w = __expf(v.w - m);
+        sc4[i] = v;
+        l += (v.x + v.y) + (v.z + v.w);
     }
     l = warp_sum(l);
     if (lane == 0) sm.misc[4 + warp] = l;
     __syncthreads();
     l = (sm.misc[4] + sm.misc[5]) + (sm.misc[6] + sm.misc[7]);
 
+    PHASE(3);
     // ---- 3. p.V -----------------------------------------------------------------------------------
-    {
-        if (t0 < v_hi) pv_packed_mma<VB, 2>(a, vc, vs, vz, sm, t0, v_hi);
-        const int lo = max(t0, a.Tvq);
-        if (lo < t1) {
-            const __half *vf = static_cast<const __half *>(a.vfull) + (int64_t)b * a.vf_sB + (int64_t)hk * a.vf_sH;
-            const int co = tid & 15, tl = tid >> 4;           // 8 channels per thread, 8 token lanes per CTA
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int t = lo + tl; t < t1; t += 8) {
-                int s0 = a.vf_start + (t - a.Tvq);
-                if (s0 >= a.vf_cap) s0 -= a.vf_cap;
-                const uint4 u = __ldg(reinterpret_cast<const uint4 *>(vf + (int64_t)s0 * a.vf_sT) + co);
-                const float p = sm.scores[t - t0];
-                const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+    if (v_lo < t1) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int base = v_lo; base < t1; base += 128) {
+            if (base > v_lo) load_tail_round(base);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int t = base + tl + 8 * j;
+                const float p = (t < t1) ? sm.scores[t - t0] : 0.f;
+                const __half2 *h = reinterpret_cast<const __half2 *>(&vt[j]);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const float2 f = __half22float2(h[k]);
@@ -776,16 +893,19 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
                     acc[2 * k + 1] = fmaf(p, f.y, acc[2 * k + 1]);
                 }
             }
+        }
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 16);   // the warp's two token lanes
-            if (lane < 16) {
-                float4 *dst = reinterpret_cast<float4 *>(sm.tailred + warp * kHeadDim + 8 * co);
-                dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-            }
+        for (int k = 0; k < 8; ++k) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 16);   // the warp's two token lanes
+        if (lane < 16) {
+            float4 *dst = reinterpret_cast<float4 *>(sm.tailred + warp * kHeadDim + 8 * co);
+            dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
         }
     }
+    PHASE(4);
+    if (t0 < v_hi) pv_packed_mma<VB, 2>(a, vc, vs, vz, sm, t0, v_hi);
     __syncthreads();
+    PHASE(5);
 
     // ---- 4. finish / merge (same protocol as the generic kernel) ------------------------------------
     float o = (sm.tailred[tid] + sm.tailred[kHeadDim + tid]) + (sm.tailred[2 * kHeadDim + tid] + sm.tailred[3 * kHeadDim + tid]);
@@ -803,12 +923,16 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
     float *part = parts + ((int64_t)s * n_splits + split) * kPart;
     part[tid] = o;
     if (tid == 0) { part[kHeadDim] = m; part[kHeadDim + 1] = l; }
-    __threadfence();
     __syncthreads();
-    if (tid == 0) sm.misc[8] = (atomicAdd(&counters[s], 1u) == (unsigned)(n_splits - 1)) ? 1.f : 0.f;
+    if (tid == 0) {
+        // one cumulative device-scope fence after the CTA barrier publishes every thread's partial before the count;
+        // the fence after the count orders the merging CTA's reads (ld.cg, from L2) behind the other CTAs' fences
+        __threadfence();
+        sm.misc[8] = (atomicAdd(&counters[s], 1u) == (unsigned)(n_splits - 1)) ? 1.f : 0.f;
+        __threadfence();
+    }
     __syncthreads();
     if (sm.misc[8] == 0.f) return;
-    __threadfence();
     const float *base = parts + (int64_t)s * n_splits * kPart;
     float M = -3.0e38f;
     for (int i = 0; i < n_splits; ++i) M = fmaxf(M, __ldcg(base + i * kPart + kHeadDim));
@@ -852,7 +976,8 @@ bool mma_path_eligible(const kvq_attn_args &a) {
 template <int KB, int VB>
 static int launch_mma(const kvq_attn_args &a, int chunk, int n_splits, float *parts, unsigned int *counters,
                       cudaStream_t st) {
-    int n_scores = chunk < a.T ? chunk : a.T;
+    const int last = a.T - (n_splits - 1) * chunk;            // the last split runs to T
+    int n_scores = (n_splits > 1 && chunk > last) ? chunk : last;
     n_scores = (n_scores + 31) / 32 * 32;
     const size_t smem = (size_t)n_scores * 4 + (size_t)kMmaWarps * warp_region_bytes<KB, VB>() +
                         kMmaWarps * kHeadDim * 4 + kHeadDim * 2 + 16 * 4;
@@ -878,3 +1003,6 @@ int launch_decode_attn_mma(const kvq_attn_args &a, int chunk, int n_splits, floa
 }
 
 }  // namespace kvq
+#ifdef KVQ_PHASE_TIMING
+extern "C" int kvq_debug_phases(unsigned long long *dst) { return (int)cudaMemcpyFromSymbol(dst, kvq::g_phase, sizeof(kvq::g_phase)); }
+#endif

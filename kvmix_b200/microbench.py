@@ -5,6 +5,8 @@ stand-alone quantize-on-append sweep.
     python -m kvmix_b200.microbench quant BITS G STYLE [B] [T] [reps]  STYLE k: [B,32,T,128] keys, groups over tokens
                                                                        STYLE v: values, groups over channels
     python -m kvmix_b200.microbench quant-sweep                        the sweep of benchmark configuration 4
+    python -m kvmix_b200.microbench phases KB VB G [B] [T]             per-CTA phase durations of the attention kernel
+                                                                       (needs `python -m kvmix_b200.build --phase-timing`)
 
 Each line reports microseconds per launch and algorithmic GB/s (bytes the operator must move / time).
 """
@@ -43,6 +45,41 @@ def attn(kb, vb, G, B=16, T=4096, reps=3, heads=32, kv_heads=None, window=128):
     print(f"attn K{kb}V{vb} G{G} B{B} H{heads}/{kv_heads} T{T}: {ms * 1e3:.1f} us/launch, {by / 1e6:.1f} MB, "
           f"{by / ms / 1e6:.0f} GB/s")
     return by / ms / 1e6
+
+
+def phases(kb, vb, G, B=64, T=4096, heads=32):
+    """Mean / p10 / p90 duration of each phase of the tensor-core attention kernel over its first 4096 CTAs, from the
+    kernel's optional %globaltimer stamps (the per-line view of a profiler's source page is not used in this project)."""
+    import ctypes
+
+    import numpy as np
+
+    from . import _lib
+    lib = _lib.lib()
+    if not hasattr(lib, "kvq_debug_phases"):
+        raise SystemExit("the library was built without the phase clock: python -m kvmix_b200.build --phase-timing")
+    dev = torch.device("cuda:0")
+    c = KVmixLayerCache(B, heads, 128, T + 64, kb, vb, G, residual_length=128, device=dev)
+    k, v = configs.synth_kv(B, heads, T, 128, dev, 0)
+    c.prefill(k, v)
+    del k, v
+    q = torch.randn((B, heads, 1, 128), device=dev, dtype=torch.float16)
+    out = torch.empty_like(q)
+    for _ in range(3):
+        c.attend(q, out=out)
+    torch.cuda.synchronize()
+    buf = np.zeros(4096 * 8, dtype=np.uint64)
+    if lib.kvq_debug_phases(buf.ctypes.data_as(ctypes.c_void_p)) != 0:
+        raise SystemExit("could not read the phase stamps")
+    p = buf.reshape(4096, 8)[:, :6].astype(np.int64)
+    p = p[(p[:, 0] > 0) & (p[:, 5] > 0)]
+    d = np.diff(p, axis=1) / 1000.0
+    print(f"phases K{kb}V{vb} G{G} B{B} T{T}: {len(p)} CTAs, mean life {(p[:, 5] - p[:, 0]).mean() / 1000:.1f} us, "
+          f"first start to last end {(p[:, 5].max() - p[:, 0].min()) / 1000:.1f} us")
+    for i, name in enumerate(["q store", "scores (packed + fp16 tail keys)", "softmax (+ tail value loads)",
+                              "fp16 tail values", "packed values"]):
+        print(f"  {name:34s} mean {d[:, i].mean():6.2f} us  p10 {np.percentile(d[:, i], 10):6.2f}  "
+              f"p90 {np.percentile(d[:, i], 90):6.2f}")
 
 
 def quant(bits, G, style, B=16, T=8192, reps=3, heads=32):
@@ -96,6 +133,8 @@ if __name__ == "__main__":
         attn(*[int(x) for x in a[1:]])
     elif a[0] == "quant":
         quant(int(a[1]), int(a[2]), a[3], *[int(x) for x in a[4:]])
+    elif a[0] == "phases":
+        phases(*[int(x) for x in a[1:]])
     elif a[0] == "quant-sweep":
         quant_sweep()
     else:
