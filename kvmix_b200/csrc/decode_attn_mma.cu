@@ -250,8 +250,17 @@ __device__ __forceinline__ unsigned long long gtime() {
     return t;
 }
 #define PHASE(i) do { if (threadIdx.x == 0 && blockIdx.x < 4096) g_phase[blockIdx.x * 8 + (i)] = gtime(); } while (0)
+// slots 6 / 7: nanoseconds warp 0 spent waiting for its key / value ring (cp.async.wait_group + warp barrier)
+#define STALL_DECL unsigned long long stall_ns = 0
+#define STALL_BEGIN const unsigned long long stall_t0 = gtime()
+#define STALL_END stall_ns += gtime() - stall_t0
+#define STALL_STORE(i) do { if (threadIdx.x == 0 && blockIdx.x < 4096) g_phase[blockIdx.x * 8 + (i)] = stall_ns; } while (0)
 #else
 #define PHASE(i)
+#define STALL_DECL
+#define STALL_BEGIN
+#define STALL_END
+#define STALL_STORE(i)
 #endif
 struct MmaSmem {
     float *scores;          // [n_scores]
@@ -345,6 +354,7 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     if (tail_lo < t1) qk_tail_mma(a, kf, sm, t0, tail_lo, t1);
 
     const uint32_t ones = 0x3c003c00u;
+    STALL_DECL;
     for (int j = 0; j < my_tiles; ++j) {
         const int tile0 = t0 + (j * kMmaWarps + warp) * G::WT;
         const bool have_next = j + 1 < my_tiles;
@@ -352,8 +362,12 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
         const bool ok_nxt = have_next && (wcol_cur + tile_words < n_words);
 
         // the scale/zero tile of this warp tile was committed at least 3 groups ago
-        cp_async_wait<2>();
-        __syncwarp();
+        {
+            STALL_BEGIN;
+            cp_async_wait<2>();
+            __syncwarp();
+            STALL_END;
+        }
         // ---- B fragments q*scale and the zero term sum_d q[d]*zero[d,g] ----------------------------------
         // q*scale needs 22 bits; it is carried as an fp16 pair hi + lo (lo = fma(q, s, -hi) is exact), so the key
         // side adds no rounding beyond the fp32 accumulation.  The zero term gets the same treatment and is summed
@@ -416,8 +430,12 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
             }
             if (st == 0 && have_next) issue_sz(ks_cur + tile_groups, kz_cur + tile_groups);
             cp_async_commit();
-            cp_async_wait<G::P>();
-            __syncwarp();
+            {
+                STALL_BEGIN;
+                cp_async_wait<G::P>();
+                __syncwarp();
+                STALL_END;
+            }
             const uint32_t src = frag_s + (st % G::NS) * G::STAGE_BYTES;
 #pragma unroll
             for (int k = 0; k < G::KSPS; ++k) {
@@ -529,6 +547,7 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
         kz_cur += tile_groups;
     }
     cp_async_wait<0>();
+    STALL_STORE(6);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -609,6 +628,7 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     };
 
     float acc[8][4], accz[4] = {0.f, 0.f, 0.f, 0.f};
+    STALL_DECL;
 #pragma unroll
     for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
     const uint32_t ones = 0x3c003c00u;
@@ -648,8 +668,12 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     for (int q = 0; q < my_blocks; ++q) {
         issue_stage(issue_st);
         cp_async_commit();
-        cp_async_wait<G::P>();
-        __syncwarp();
+        {
+            STALL_BEGIN;
+            cp_async_wait<G::P>();
+            __syncwarp();
+            STALL_END;
+        }
         // ---- B operands for the stage: 16 token pairs x 8 columns -----------------------------------
         {
             // p is scaled by 2^8 before the fp16 rounding so that the many small probabilities of a long, diffuse
@@ -708,6 +732,7 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     flush();
     cp_async_wait<0>();
     __syncwarp();
+    STALL_STORE(7);
     // epilogue: channel c = 16 g + i (i = 2m + r); columns 2*grp (sum p*scale) and 2*grp+1 (sum p*mid) sit in tig == grp
     if (tig == grp) {
         float *red = my_red + 16 * g;

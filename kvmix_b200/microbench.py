@@ -71,8 +71,9 @@ def phases(kb, vb, G, B=64, T=4096, heads=32):
     buf = np.zeros(4096 * 8, dtype=np.uint64)
     if lib.kvq_debug_phases(buf.ctypes.data_as(ctypes.c_void_p)) != 0:
         raise SystemExit("could not read the phase stamps")
-    p = buf.reshape(4096, 8)[:, :6].astype(np.int64)
-    p = p[(p[:, 0] > 0) & (p[:, 5] > 0)]
+    raw = buf.reshape(4096, 8).astype(np.int64)
+    raw = raw[(raw[:, 0] > 0) & (raw[:, 5] > 0)]
+    p = raw[:, :6]
     d = np.diff(p, axis=1) / 1000.0
     print(f"phases K{kb}V{vb} G{G} B{B} T{T}: {len(p)} CTAs, mean life {(p[:, 5] - p[:, 0]).mean() / 1000:.1f} us, "
           f"first start to last end {(p[:, 5].max() - p[:, 0].min()) / 1000:.1f} us")
@@ -80,6 +81,7 @@ def phases(kb, vb, G, B=64, T=4096, heads=32):
                               "fp16 tail values", "packed values"]):
         print(f"  {name:34s} mean {d[:, i].mean():6.2f} us  p10 {np.percentile(d[:, i], 10):6.2f}  "
               f"p90 {np.percentile(d[:, i], 90):6.2f}")
+    print(f"  warp 0 waiting on its ring: keys {raw[:, 6].mean() / 1000:6.2f} us, values {raw[:, 7].mean() / 1000:6.2f} us")
 
 
 def quant(bits, G, style, B=16, T=8192, reps=3, heads=32):
