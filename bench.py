@@ -29,9 +29,9 @@ SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.acti
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
 
-# DRAM traffic per (sequence, head) unit of one fused-attention launch, dram__bytes_read+write from the ncu
-# captures summarised in profiles/decode_attn_mma_kernel_B16_ctx4096.md (B=16 case; traffic is proportional to units).
-NCU_TRAFFIC_PER_UNIT = {(4, 4): 737.5e3, (3, 2): 660.0e3, (2, 2): 470.7e3}
+# DRAM traffic per (sequence, head) unit of one fused-attention launch: dram__bytes_read + dram__bytes_write of an
+# ncu capture of each kernel variant at B=32, context 4096 (one CTA per unit, so traffic is proportional to units).
+NCU_TRAFFIC_PER_UNIT = {(4, 4): 739.3e3, (3, 2): 657.5e3, (2, 2): 469.8e3}
 
 
 def measured_peak_gbs():
@@ -323,7 +323,7 @@ def main():
                          "peak_source": peak_src,
                          "traffic": (sum(NCU_TRAFFIC_PER_UNIT[(q["k_bits"], q["v_bits"])]
                                          for q in cfg.quant_bits.values()) / L * B * nh) if args.config == 2 else None,
-                         "traffic_note": "bytes per launch (layer average), ncu dram read+write of a B=16 capture scaled by units",
+                         "traffic_note": "bytes per launch (layer average), ncu dram read+write of a B=32 capture scaled by units",
                          "bytes_per_launch": attn_bytes_all / max(1, n_attn),
                          "us_per_launch": attn_ms_all * 1e3 / max(1, n_attn), "launches_timed": n_attn,
                          "attention_share_of_step": attn_ms_all / ms_total},

@@ -85,7 +85,7 @@ static SplitPlan plan_splits_mma(int T, int k_bits, int64_t heads) {
         const double longest = chunk > last ? chunk : last;
         double rate = q / waves * ((double)T / n) / (longest + kMmaCtaCost);
         if (longest < 4096) rate *= 0.9;
-        if (n > 1) rate *= 0.97;
+        if (n > 1) rate *= 0.92;
         if (rate > best_rate * 1.0001) {
             best = {chunk, n};
             best_rate = rate;
