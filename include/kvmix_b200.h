@@ -169,6 +169,13 @@ int kvq_gemv(const kvq_gemv_args *a, kvq_stream_t stream);
  * round_scores != 0 narrows each raw score to fp16 before scaling, as upstream's GEMV and fp16
  * matmul do; everything else accumulates in fp32.
  *
+ * mask (optional, NULL = none): additive attention mask over the T key positions, as the upstream forward
+ * applies it (models/modeling_llama_KVmix.py:188-193: weights + mask, then clamped from below at the most
+ * negative finite fp32, then softmax).  mask[b*mask_sB + h*mask_sH + t], fp16 (mask_is_f32 == 0) or fp32;
+ * mask_sH = 0 broadcasts one row over the heads (the usual [B,1,1,T] padding mask).  Position t counts the
+ * packed prefix first and the fp16 tail after it, i.e. chronological order, so a left-padding mask indexes
+ * it directly.
+ *
  * workspace: kvq_decode_attn_workspace_bytes(B, nh, T) bytes of device memory (split partials and
  * one counter per query head).  The call zeroes the counters itself; concurrent calls must not
  * share a workspace.
@@ -201,6 +208,9 @@ typedef struct {
     int32_t vf_cap, vf_start;
     void *workspace;
     uint64_t workspace_bytes;
+    const void *mask;
+    int64_t mask_sB, mask_sH;
+    int32_t mask_is_f32;
 } kvq_attn_args;
 
 uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32_t T);

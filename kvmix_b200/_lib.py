@@ -53,7 +53,8 @@ class AttnArgs(C.Structure):
                 ("vscale", vp), ("vmn", vp), ("vs_sB", i64), ("vs_sH", i64), ("vs_sT", i64),
                 ("vfull", vp), ("vf_sB", i64), ("vf_sH", i64), ("vf_sT", i64),
                 ("vf_cap", i32), ("vf_start", i32),
-                ("workspace", vp), ("workspace_bytes", u64)]
+                ("workspace", vp), ("workspace_bytes", u64),
+                ("mask", vp), ("mask_sB", i64), ("mask_sH", i64), ("mask_is_f32", i32)]
 
 
 _lib = None

@@ -167,8 +167,10 @@ class KVmixLayerCache:
         self._absorb_ring()
 
     # -- attention -----------------------------------------------------------------------------------
-    def attend(self, q, out=None, round_scores=True):
-        """q: [B,nh,1,D] fp16 -> [B,nh,1,D] fp16 over everything cached (upstream :170-211)."""
+    def attend(self, q, out=None, round_scores=True, attention_mask=None):
+        """q: [B,nh,1,D] fp16 -> [B,nh,1,D] fp16 over everything cached (upstream :170-211).  attention_mask:
+        optional additive mask over the kv_seq_len cached positions ([B,1,1,T], [B,nh,1,T] or [B,T]; upstream
+        :188-193), e.g. the left-padding mask of a ragged batch."""
         B, nh, M, D = q.shape
         if M != 1 or B != self.B or D != self.D or not q.is_cuda:
             raise RuntimeError("attend takes q [B, nh, 1, D] on the cache's device")
@@ -190,13 +192,14 @@ class KVmixLayerCache:
         a.out, a.o_sB, a.o_sH = out.data_ptr(), out.stride(0), out.stride(1)
         a.kf_start, a.vf_start = self.k_start, self.v_start
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        a.mask, a.mask_sB, a.mask_sH, a.mask_is_f32 = ops.mask_fields(attention_mask, B, nh, a.T)
         _lib.check(self._lib.kvq_decode_attn(C.byref(a), C.c_void_p(stream)))
         ops.LAUNCHES[0] += 1
         return out
 
-    def decode_step(self, q, k_new, v_new, out=None):
+    def decode_step(self, q, k_new, v_new, out=None, attention_mask=None):
         self.append(k_new, v_new)
-        return self.attend(q, out=out)
+        return self.attend(q, out=out, attention_mask=attention_mask)
 
     # -- export in upstream's layout -----------------------------------------------------------------
     def _ring(self, buf, start, n, cap):
@@ -260,8 +263,10 @@ def kv_bytes_per_head(tkq, tvq, rk, rv, D, k_bits, k_group, v_bits, v_group):
 
 
 def attention_step(query_states, key_states, value_states, past_key_value, k_bits, v_bits, group_size,
-                   k_residual_ratio=None, v_residual_ratio=None, residual_length=None, use_cache=True):
+                   k_residual_ratio=None, v_residual_ratio=None, residual_length=None, use_cache=True,
+                   attention_mask=None):
     """Functional drop-in for upstream's attention body (modeling_llama_KVmix.py:105-273).
+    attention_mask is upstream's additive mask ([B,1,q_len,kv_seq_len]); None means causal prefill / no padding.
 
     query_states [B,nh,q_len,D], key_states/value_states [B,Hkv,q_len,D] (after RoPE);
     past_key_value is upstream's 9-tuple or None.  Returns (attn_output [B,nh,q_len,D], new 9-tuple).
@@ -302,11 +307,11 @@ def attention_step(query_states, key_states, value_states, past_key_value, k_bit
         kfull = kfull.contiguous()
         vfull = vfull.contiguous()
         attn = ops.decode_attention(query_states, kq, ksc, kmn, kfull, vq, vsc, vmn, vfull, k_bits, k_group,
-                                    v_bits, v_group)
+                                    v_bits, v_group, attention_mask=attention_mask)
     else:
         attn = torch.nn.functional.scaled_dot_product_attention(
-            query_states, key_states, value_states, is_causal=q_len > 1, enable_gqa=nh != Hkv,
-            scale=1.0 / math.sqrt(D))
+            query_states, key_states, value_states, attn_mask=attention_mask,
+            is_causal=attention_mask is None and q_len > 1, enable_gqa=nh != Hkv, scale=1.0 / math.sqrt(D))
         kfull = kfull.contiguous()
         vfull = vfull.contiguous()
     new_past = (kq, kfull, ksc, kmn, vq, vfull, vsc, vmn, kv_seq_len) if use_cache else None

@@ -38,6 +38,15 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // Records the text of the last failing CUDA call for kvq_last_cuda_error().
+// Additive attention mask value for (sequence b, query head h, key position t); the caller checked a.mask != NULL.
+__device__ __forceinline__ float attn_mask_at(const kvq_attn_args &a, int b, int h, int t) {
+    const int64_t off = (int64_t)b * a.mask_sB + (int64_t)h * a.mask_sH + t;
+    return a.mask_is_f32 ? __ldg(static_cast<const float *>(a.mask) + off)
+                         : __half2float(__ldg(static_cast<const __half *>(a.mask) + off));
+}
+// upstream clamps masked weights from below at torch.finfo(float32).min (models/modeling_llama_KVmix.py:192)
+constexpr float kMaskFloor = -3.4028234663852886e38f;
+
 int record_cuda_error(cudaError_t e);
 inline int check_launch() { return record_cuda_error(cudaGetLastError()); }
 

@@ -229,8 +229,16 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(kvq_attn_args
 
     // ---- 2. softmax numerators over this split ------------------------------------------------
     const int n = t1 - t0;
-    float m = -3.0e38f;
-    for (int i = tid; i < n; i += kAttnThreads) m = fmaxf(m, sm.scores[i]);
+    float m = kMaskFloor;                                      // a fully masked range then weighs uniformly, as upstream's does
+    if (a.mask) {                                              // weights + mask, clamped at the fp32 floor
+        for (int i = tid; i < n; i += kAttnThreads) {
+            const float v = fmaxf(sm.scores[i] + attn_mask_at(a, b, h, t0 + i), kMaskFloor);
+            sm.scores[i] = v;
+            m = fmaxf(m, v);
+        }
+    } else {
+        for (int i = tid; i < n; i += kAttnThreads) m = fmaxf(m, sm.scores[i]);
+    }
     m = warp_max(m);
     if (lane == 0) sm.warp_red[warp] = m;
     __syncthreads();
@@ -313,7 +321,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(kvq_attn_args
     if (!sm.last) return;
     __threadfence();
     const float *base = parts + (int64_t)s * n_splits * kPartStride;
-    float M = -3.0e38f;
+    float M = kMaskFloor;
     for (int i = 0; i < n_splits; ++i) M = fmaxf(M, __ldcg(base + i * kPartStride + kHeadDim));
     if (tid < kHeadDim) {
         float L = 0.f, acc = 0.f;

@@ -866,16 +866,24 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
     };
     if (v_lo < t1) load_tail_round(v_lo);
 
-    float m = -3.0e38f;
+    float m = kMaskFloor;                                      // a fully masked range then weighs uniformly, as upstream's does
     const int n4 = (n + 3) >> 2;
     float4 *sc4 = reinterpret_cast<float4 *>(sm.scores);
 #pragma unroll 4
     for (int i = tid; i < n4; i += kMmaThreads) {
         float4 v = sc4[i];
+        if (a.mask) {                                          // weights + mask, clamped at the fp32 floor
+            const int t = t0 + 4 * i;
+            v.x = fmaxf(v.x + attn_mask_at(a, b, h, min(t, a.T - 1)), kMaskFloor);
+            v.y = fmaxf(v.y + attn_mask_at(a, b, h, min(t + 1, a.T - 1)), kMaskFloor);
+            v.z = fmaxf(v.z + attn_mask_at(a, b, h, min(t + 2, a.T - 1)), kMaskFloor);
+            v.w = fmaxf(v.w + attn_mask_at(a, b, h, min(t + 3, a.T - 1)), kMaskFloor);
+            sc4[i] = v;
+        }
         if (4 * i + 3 >= n) {                                  // the last, partial quad: neutral padding
-            if (4 * i + 1 >= n) v.y = -3.0e38f;
-            if (4 * i + 2 >= n) v.z = -3.0e38f;
-            v.w = -3.0e38f;
+            if (4 * i + 1 >= n) v.y = -INFINITY;
+            if (4 * i + 2 >= n) v.z = -INFINITY;
+            v.w = -INFINITY;
             sc4[i] = v;
         }
         m = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
@@ -959,7 +967,7 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
     __syncthreads();
     if (sm.misc[8] == 0.f) return;
     const float *base = parts + (int64_t)s * n_splits * kPart;
-    float M = -3.0e38f;
+    float M = kMaskFloor;
     for (int i = 0; i < n_splits; ++i) M = fmaxf(M, __ldcg(base + i * kPart + kHeadDim));
     float L = 0.f, acc = 0.f;
     for (int i = 0; i < n_splits; ++i) {

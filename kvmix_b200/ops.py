@@ -234,10 +234,34 @@ def _ptr(t):
     return 0 if t is None else t.data_ptr()
 
 
+def mask_fields(mask, B, nh, T):
+    """(pointer, batch stride, head stride, is_f32) of an additive attention mask for kvq_attn_args; the caller
+    keeps `mask` alive until the launch is enqueued.  Accepts [B,T], [B,1,1,T] or [B,nh,1,T]."""
+    if mask is None:
+        return 0, 0, 0, 0
+    _need_cuda(mask)
+    if mask.dtype not in (torch.float16, torch.float32):
+        raise RuntimeError("attention_mask must be float16 or float32")
+    if mask.dim() == 4:
+        if mask.shape[2] != 1:
+            raise RuntimeError(f"Attention mask shape {tuple(mask.shape)} does not match weights shape {(B, nh, 1, T)}")
+        mask = mask[:, :, 0, :]
+    elif mask.dim() == 2:
+        mask = mask[:, None, :]
+    if mask.dim() != 3 or mask.shape[0] != B or mask.shape[1] not in (1, nh) or mask.shape[2] != T:
+        raise RuntimeError(f"Attention mask shape {tuple(mask.shape)} does not match weights shape {(B, nh, 1, T)}")
+    if mask.stride(2) != 1:
+        raise RuntimeError("attention_mask must be contiguous along the key positions")
+    return mask.data_ptr(), mask.stride(0), (0 if mask.shape[1] == 1 else mask.stride(1)), int(mask.dtype == torch.float32)
+
+
 def decode_attention(q, kcode, kscale, kmn, kfull, vcode, vscale, vmn, vfull, k_bits, k_group, v_bits, v_group,
                      Tkq=None, Tvq=None, Rk=None, Rv=None, kf_start=0, vf_start=0, round_scores=True, out=None,
-                     workspace=None, softmax_scale=None):
+                     workspace=None, softmax_scale=None, attention_mask=None):
     """Fused decode attention (one launch) over [packed prefix | fp16 tail] keys and values.
+
+    attention_mask: optional additive mask over the T key positions, [B,1,1,T] / [B,nh,1,T] / [B,T], fp16 or
+    fp32 (upstream models/modeling_llama_KVmix.py:188-193: added to the scaled scores, clamped at the fp32 floor).
 
     q [B,nh,1,D] fp16.  kcode [B,Hkv,D,>=Tkq/fpi], kscale/kmn [B,Hkv,D,>=Tkq/Gk]; kfull
     [B,Hkv,cap,D] holding Rk tokens starting at row kf_start (ring).  vcode [B,Hkv,>=Tvq,D/fpi],
@@ -278,7 +302,7 @@ def decode_attention(q, kcode, kscale, kmn, kfull, vcode, vscale, vmn, vfull, k_
                  _ptr(vscale), _ptr(vmn), _s(vscale, 0), _s(vscale, 1), _s(vscale, 2),
                  _ptr(vfull), _s(vfull, 0), _s(vfull, 1), _s(vfull, 2),
                  0 if vfull is None else vfull.shape[2], vf_start,
-                 workspace.data_ptr(), workspace.numel())
+                 workspace.data_ptr(), workspace.numel(), *mask_fields(attention_mask, B, nh, T))
     check(_lib.lib().kvq_decode_attn(C.byref(a), _stream()))
     LAUNCHES[0] += 1
     return out

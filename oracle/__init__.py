@@ -144,8 +144,9 @@ def process_value_quantization(x, prev_code, prev_scale, prev_mn, group_length, 
 
 
 def decode_attention(q, kcode, kscale, kmn, kfull, vcode, vscale, vmn, vfull, k_bits, k_group, v_bits,
-                     v_group, ref_rounding=True):
+                     v_group, ref_rounding=True, attention_mask=None):
     """Cached-branch attention of one query token (models/modeling_llama_KVmix.py:170-211).
+    attention_mask: optional additive mask [B,1,1,T] or [B,nh,1,T] (upstream :188-193).
 
     q [B,nh,1,D]; kcode [B,Hkv,D,Tkq/fpi] (or None), kfull [B,Hkv,Rk,D]; vcode [B,Hkv,Tvq,D/fpi]
     (or None), vfull [B,Hkv,Rv,D].  Returns [B,nh,1,D] fp16.
@@ -163,8 +164,13 @@ def decode_attention(q, kcode, kscale, kmn, kfull, vcode, vscale, vmn, vfull, k_
     arrs = [np.ascontiguousarray(a) for a in arrs]
     out = np.empty((B, nh, 1, D), np.float16)
     i64 = ctypes.c_int64
+    if attention_mask is not None:
+        m = np.ascontiguousarray(np.asarray(attention_mask, np.float32).reshape(B, -1, Tkq + Rk))
+        mp, mh = _p(m), m.shape[1]
+    else:
+        mp, mh = None, 1
     rc = lib().orc_decode_attn(*[_p(a) for a in arrs], i64(B), i64(nh), i64(Hkv), i64(D), i64(Tkq), i64(Rk),
                                i64(Tvq), i64(Rv), k_bits, k_group, v_bits, v_group, (7 if ref_rounding is True else int(ref_rounding)),
-                               _p(out))
+                               mp, i64(mh), _p(out))
     _check(rc)
     return out

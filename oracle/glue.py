@@ -69,15 +69,15 @@ class RefLayerCache:
         self._absorb()
 
     # -- attention ---------------------------------------------------------------------------
-    def attend(self, q, ref_rounding=True):
-        """q: [B, nh, 1, D] fp16 -> [B, nh, 1, D] fp16 (:170-211)."""
+    def attend(self, q, ref_rounding=True, attention_mask=None):
+        """q: [B, nh, 1, D] fp16 -> [B, nh, 1, D] fp16 (:170-211); attention_mask as upstream's (:188-193)."""
         return decode_attention(q, self.kcode, self.kscale, self.kmn, self.kfull, self.vcode, self.vscale,
                                 self.vmn, self.vfull, self.k_bits, self.k_group, self.v_bits, self.v_group,
-                                ref_rounding)
+                                ref_rounding, attention_mask=attention_mask)
 
-    def decode_step(self, q, k_new, v_new, ref_rounding=True):
+    def decode_step(self, q, k_new, v_new, ref_rounding=True, attention_mask=None):
         self.append(k_new, v_new)
-        return self.attend(q, ref_rounding)
+        return self.attend(q, ref_rounding, attention_mask=attention_mask)
 
     @property
     def tkq(self):

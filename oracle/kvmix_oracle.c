@@ -321,7 +321,8 @@ int orc_append_v_f16(const h16 *xnew, int64_t bh, int64_t Tn, int64_t D, const i
 int orc_decode_attn(const h16 *q, const int32_t *kcode, const h16 *kscale, const h16 *kmn, const h16 *kfull,
                     const int32_t *vcode, const h16 *vscale, const h16 *vmn, const h16 *vfull, int64_t B,
                     int64_t nh, int64_t nh_kv, int64_t D, int64_t Tkq, int64_t Rk, int64_t Tvq, int64_t Rv,
-                    int kbits, int Gk, int vbits, int Gv, int ref_rounding, h16 *out) {
+                    int kbits, int Gk, int vbits, int Gv, int ref_rounding, const float *mask, int64_t mask_heads,
+                    h16 *out) {
     if (Tkq + Rk != Tvq + Rv) return -9;
     if (nh % nh_kv) return -6;
     if (vbits == 3 && D % 11) return -3;     /* quantization_cuda.cu:433-434: upstream cannot hold such V */
@@ -361,7 +362,13 @@ int orc_decode_attn(const h16 *q, const int32_t *kcode, const h16 *kscale, const
                 sc[Tkq + r] = (ref_rounding & 1) ? h2f(f2h(a)) : a;                                /* R2 */
             }
             float mx = -FLT_MAX;
-            for (int64_t t = 0; t < T; ++t) { sc[t] = sc[t] / sqrtf((float)D); mx = fmaxf(mx, sc[t]); } /* R3 */
+            /* additive mask [B, mask_heads (1 or nh), T], then clamp at finfo(float32).min: modeling_llama_KVmix.py:188-192 */
+            const float *mrow = mask ? mask + (b * mask_heads + (mask_heads == 1 ? 0 : h)) * T : 0;
+            for (int64_t t = 0; t < T; ++t) {
+                sc[t] = sc[t] / sqrtf((float)D);                                                     /* R3 */
+                if (mrow) sc[t] = fmaxf(sc[t] + mrow[t], -FLT_MAX);
+                mx = fmaxf(mx, sc[t]);
+            }
             float sum = 0.0f;
             for (int64_t t = 0; t < T; ++t) { sc[t] = expf(sc[t] - mx); sum += sc[t]; }
             for (int64_t t = 0; t < T; ++t) {

@@ -6,7 +6,7 @@ import torch
 
 import oracle
 from oracle.glue import RefLayerCache
-from util import assert_attn_close, assert_attn_parity, assert_close_to_upstream, make_kv, make_q
+from util import REL_TOL, assert_attn_close, assert_attn_parity, assert_close_to_upstream, make_kv, make_q
 
 pytestmark = pytest.mark.gpu
 
@@ -171,3 +171,79 @@ def test_attention_argument_errors(cuda):
     with pytest.raises(RuntimeError, match="not supported"):
         kv.decode_attention(z(1, 2, 1, 64), None, None, None, z(1, 2, 5, 64), None, None, None, z(1, 2, 5, 64),
                             4, 32, 4, 32)
+
+
+def _pad_mask(B, T, starts, dtype):
+    m = np.zeros((B, 1, 1, T), dtype)
+    for b, s in enumerate(starts):
+        m[b, 0, 0, :s] = np.finfo(dtype).min
+    return m
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kb,vb,G,nh,hkv,T", [(4, 4, 32, 4, 4, 1500), (2, 2, 32, 8, 2, 2600), (3, 2, 64, 4, 4, 1200),
+                                              (4, 2, 128, 4, 1, 9000)])
+@pytest.mark.parametrize("mdtype", [np.float16, np.float32])
+def test_left_padding_mask(cuda, kb, vb, G, nh, hkv, T, mdtype):
+    """Additive attention mask (upstream models/modeling_llama_KVmix.py:188-193) on both kernels: ragged batch with
+    per-sequence padding (none, inside the packed prefix, past a whole split, all but the fp16 window)."""
+    B = 4
+    k, v = make_kv(21, B, hkv, T)
+    q = make_q(21, B, nh)
+    ref = RefLayerCache(kb, vb, G, residual_length=128)
+    ref.prefill(k, v)
+    starts = [0, 37, min(T - 200, 4500), T - 100]
+    mask = _pad_mask(B, T, starts, mdtype)
+    md = _t(mask, cuda)
+    want32 = ref.attend(q, ref_rounding=0, attention_mask=mask)
+    want_up = ref.attend(q, ref_rounding=7, attention_mask=mask)
+    # generic kernel (upstream-shaped, unpadded tensors) and tensor-core kernel (preallocated aligned cache)
+    import kvmix_b200 as kv
+    dut = kv.KVmixLayerCache(B, hkv, 128, T + 64, kb, vb, G, device=cuda, residual_length=128,
+                             max_tail=max(ref.kfull.shape[2], ref.vfull.shape[2]) + 8)
+    dut.load_tuple(tuple(_t(x, cuda) for x in (ref.kcode, ref.kfull, ref.kscale, ref.kmn, ref.vcode, ref.vfull,
+                                               ref.vscale, ref.vmn)) + (T,))
+    for run in (lambda rs: _attend_gpu(ref, q, cuda, round_scores=rs, attention_mask=md),
+                lambda rs: dut.attend(_t(q, cuda), round_scores=rs, attention_mask=md).cpu().numpy(),
+                lambda rs: dut.attend(_t(q, cuda), round_scores=rs, attention_mask=md[:, 0, 0, :]).cpu().numpy()):
+        assert_attn_close(run(False), want32, REL_TOL)
+        assert_close_to_upstream(run(True), want_up, want32)
+    # no-op mask leaves the result bit-identical; a per-head mask is honoured
+    z = torch.zeros((B, 1, 1, T), dtype=torch.float16, device=cuda)
+    assert torch.equal(dut.attend(_t(q, cuda), attention_mask=z), dut.attend(_t(q, cuda)))
+    per_head = md.expand(B, nh, 1, T).clone()
+    per_head[:, 0, 0, : T // 2] = float(np.finfo(mdtype).min)
+    mh = per_head.cpu().numpy()
+    got = dut.attend(_t(q, cuda), round_scores=False, attention_mask=per_head).cpu().numpy()
+    assert_attn_close(got, ref.attend(q, ref_rounding=0, attention_mask=mh), REL_TOL)
+
+
+@pytest.mark.gpu
+def test_fully_masked_sequence_is_uniform_like_upstream(cuda):
+    import kvmix_b200 as kv
+    T, B, nh = 2304, 2, 4
+    k, v = make_kv(22, B, nh, T)
+    q = make_q(22, B, nh)
+    ref = RefLayerCache(2, 2, 32, residual_length=128)
+    ref.prefill(k, v)
+    mask = _pad_mask(B, T, [T, 0], np.float32)
+    dut = kv.KVmixLayerCache(B, nh, 128, T + 64, 2, 2, 32, device=cuda, residual_length=128)
+    dut.load_tuple(tuple(_t(x, cuda) for x in (ref.kcode, ref.kfull, ref.kscale, ref.kmn, ref.vcode, ref.vfull,
+                                               ref.vscale, ref.vmn)) + (T,))
+    got = dut.attend(_t(q, cuda), round_scores=False, attention_mask=_t(mask, cuda)).cpu().numpy()
+    assert_attn_close(got, ref.attend(q, ref_rounding=0, attention_mask=mask), REL_TOL)
+    got = _attend_gpu(ref, q, cuda, round_scores=False, attention_mask=_t(mask, cuda))
+    assert_attn_close(got, ref.attend(q, ref_rounding=0, attention_mask=mask), REL_TOL)
+
+
+@pytest.mark.gpu
+def test_mask_shape_errors(cuda):
+    import kvmix_b200 as kv
+    k, v = make_kv(23, 1, 2, 288)
+    ref = RefLayerCache(4, 4, 32, residual_length=128)
+    ref.prefill(k, v)
+    q = make_q(23, 1, 2)
+    with pytest.raises(RuntimeError, match="does not match weights shape"):
+        _attend_gpu(ref, q, cuda, attention_mask=torch.zeros((1, 1, 1, 287), device=cuda))
+    with pytest.raises(RuntimeError, match="float16 or float32"):
+        _attend_gpu(ref, q, cuda, attention_mask=torch.zeros((1, 1, 1, 288), device=cuda, dtype=torch.bfloat16))

@@ -202,3 +202,60 @@ def test_decode_attention_against_dense(kb, vb, G, nh, hkv):
     want = np.einsum("bht,bhtd->bhd", p, V)[:, :, None]
     assert_attn_close(out_f32, want, 1e-3)
     assert_attn_close(out_ref, want, 2e-3)
+
+
+def _left_pad_mask(B, T, starts, dtype=np.float32, neg=None):
+    """Upstream's additive padding mask [B,1,1,T]: `neg` (default finfo(dtype).min) before each sequence's start."""
+    neg = np.finfo(dtype).min if neg is None else neg
+    m = np.zeros((B, 1, 1, T), dtype)
+    for b, s in enumerate(starts):
+        m[b, 0, 0, :s] = neg
+    return m
+
+
+@pytest.mark.parametrize("kb,vb,G,nh,hkv", [(4, 2, 32, 4, 4), (2, 2, 32, 4, 2), (3, 4, 32, 2, 2)])
+def test_decode_attention_mask_equals_attention_over_the_unmasked_suffix(kb, vb, G, nh, hkv):
+    """models/modeling_llama_KVmix.py:188-193: with a left-padding mask the result is attention over the
+    unmasked positions only; the oracle's masked output must equal a float64 dense evaluation of that."""
+    T, B = 352 + 128, 2
+    k, v = make_kv(9, B, hkv, T)
+    q = make_q(9, B, nh)
+    c = RefLayerCache(kb, vb, G, residual_length=128)
+    c.prefill(k, v)
+    starts = [0, 133]
+    mask = _left_pad_mask(B, T, starts)
+    got = c.attend(q, ref_rounding=0, attention_mask=mask)
+    assert np.array_equal(c.attend(q, ref_rounding=0, attention_mask=np.zeros_like(mask)), c.attend(q, ref_rounding=0))
+    assert np.array_equal(got[0], c.attend(q, ref_rounding=0)[0])           # sequence 0 has no padding
+    fk, fv = oracle.features_per_int(kb), oracle.features_per_int(vb)
+
+    def unpack(code, bits, f):
+        w = code.astype(np.int64) & 0xFFFFFFFF
+        parts = ([(w >> (3 * i)) & 7 for i in range(10)] + [w >> 30]) if bits == 3 else \
+            [(w >> (bits * i)) & (2 ** bits - 1) for i in range(f)]
+        return np.stack(parts, -1).reshape(code.shape[:-1] + (-1,))
+    kd = unpack(c.kcode, kb, fk) * np.repeat(c.kscale.astype(np.float64), c.k_group, -1) + np.repeat(c.kmn.astype(np.float64), c.k_group, -1)
+    K = np.concatenate([kd.transpose(0, 1, 3, 2), c.kfull.astype(np.float64)], 2)
+    vd = unpack(c.vcode, vb, fv) * np.repeat(c.vscale.astype(np.float64), c.v_group, -1) + np.repeat(c.vmn.astype(np.float64), c.v_group, -1)
+    V = np.concatenate([vd, c.vfull.astype(np.float64)], 2)
+    rep = nh // hkv
+    K, V = np.repeat(K, rep, 1), np.repeat(V, rep, 1)
+    s = np.einsum("bhd,bhtd->bht", q[:, :, 0].astype(np.float64), K) / np.sqrt(128.0)
+    for b, st in enumerate(starts):
+        s[b, :, :st] = -np.inf
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    want = np.einsum("bht,bhtd->bhd", p, V)[:, :, None]
+    assert_attn_close(got, want, 1e-3)
+
+
+def test_decode_attention_fully_masked_row_is_uniform():
+    """weights + mask clamped at finfo.min makes every position equal: softmax is uniform (upstream :191-193)."""
+    T = 160
+    k, v = make_kv(10, 1, 2, T)
+    q = make_q(10, 1, 2)
+    c = RefLayerCache(4, 4, 32, residual_length=128)
+    c.prefill(k, v)
+    got = c.attend(q, ref_rounding=0, attention_mask=_left_pad_mask(1, T, [T]))
+    zero_q = c.attend(np.zeros_like(q), ref_rounding=0)                      # all scores 0: uniform weights
+    assert_attn_close(got, zero_q, 1e-3)
