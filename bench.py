@@ -35,7 +35,7 @@ NCU_TRAFFIC_PER_UNIT = {(4, 4): 739.3e3, (3, 2): 657.5e3, (2, 2): 469.8e3}
 
 
 def measured_peak_gbs():
-    for p in (os.path.join(ROOT, "MEASURED_PEAKS.json"), "/root/repo/MEASURED_PEAKS.json"):
+    for p in (os.path.join(ROOT, "MEASURED_PEAKS.json"),):
         if os.path.exists(p):
             try:
                 return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"

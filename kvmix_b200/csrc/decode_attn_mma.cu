@@ -1,25 +1,27 @@
-// Fused decode attention, tensor-core path (one CTA per query head and token split; grouped queries share L2).
+// Fused decode attention, tensor-core path: one CTA (4 warps) per query head and token split; the query heads of a
+// kv head are neighbouring CTAs and share its cache through L2.
 //
-// Why tensor cores for a mat-vec: at the HBM rate a B200 has only ~1-3 issue slots per packed code
-// (2.8 per 2-bit code at 5.6 TB/s and 1.9 GHz).  Shift-mask-convert-FMA per code does not fit; one
-// logic op per *pair* of codes plus one mma.sync per 256 codes does.
+// Why tensor cores for a mat-vec: at the HBM rate a B200 has only ~1-3 issue slots per packed code (2.8 per 2-bit
+// code at 5.6 TB/s and 1.9 GHz).  Shift-mask-convert-FMA per code does not fit; one logic op per *pair* of codes
+// plus one mma.sync per 256 codes does.
 //
-// Codes go to the tensor core without ever being converted: a b-bit field left in place inside a
-// 16-bit lane, with all other bits masked off, *is* an fp16 subnormal with value field * 2^(pos-24).
-// mma.sync multiplies subnormal fp16 inputs exactly and accumulates in fp32, so the product with
-// the fp16 operand (q*scale, or p*scale) is exact and the power of two is undone per output row in
-// the epilogue.  Pairs along the contraction axis are formed with one byte-permute of two words.
+// Codes go to the tensor core without ever being converted: a b-bit field left in place inside a 16-bit lane, with
+// all other bits masked off, *is* an fp16 number with value field * 2^(pos-24) (subnormals and the first normal
+// binade are linear in the bit pattern).  mma.sync multiplies such inputs exactly and accumulates in fp32, so the
+// product with the fp16 operand is exact and the power of two is undone per output row in the epilogue.  Pairs
+// along the contraction axis are formed with one byte-permute of two words.
 //
 // Keys (codes [D, T/fpi], one word = fpi tokens of one channel; scale/zero [D, T/G]):
-//   A (16x16) = codes, rows = tokens, cols = 16 channels;  B (16x8) = q[d] * scale[d, group n]
-//   for the 8 token groups of the warp tile (one column per group of the lane-octet that owns the
-//   row), so one B fragment serves 256 tokens; the zero term  sum_d q[d]*zero[d,g]  is accumulated
-//   in fp32 on the CUDA cores once per group.  Code words and scale/zero tiles stream through a
-//   per-warp multi-stage cp.async ring in shared memory (128-bit copies, several KB in flight per warp).
+//   A (16x16) = codes, rows = tokens, cols = 16 channels.  q[d]*scale[d,g] is carried as an exact fp16 pair hi + lo.
+//   A warp tile (256 tokens; 88 for 3-bit keys) is worked as two halves whose MMA rows touch at most four groups,
+//   so B (16x8) holds {hi, lo} x 4 groups side by side and one MMA per code tile yields both parts.  The zero term
+//   sum_d q[d]*zero[d,g] (hi and lo) is summed over channels by MMAs whose A operand is all ones.
 // Values (codes [T, D/fpi], one word = fpi channels of one token; scale/zero [T, D/G]):
-//   A (16x16) = codes, rows = channels, cols = 16 tokens;  B (16x8): column 2j = p[t]*scale[t,j],
-//   column 2j+1 = p[t]*zero[t,j]; one extra MMA with A = ones sums the zero columns.
-// The fp16 tails and the softmax run on the CUDA cores as in the generic kernel.
+//   A (16x16) = codes, rows = channels, cols = 16 tokens;  B (16x8): column 2j = p[t]*scale[t,j], column 2j+1 =
+//   p[t]*midpoint[t,j] (codes are used centred on the group midpoint); one extra MMA with A = ones sums both columns.
+// Code words and scale/zero rows stream through per-warp multi-stage cp.async rings in shared memory (128-bit
+// copies, several KB in flight per warp).  The fp16 key tail is scored on the tensor cores straight from global
+// memory; the softmax, the optional additive mask and the fp16 value tail run on the CUDA cores.
 #include "common.cuh"
 
 namespace kvq {

@@ -10,8 +10,8 @@
 //
 // Three kernels, one result:
 //   quant_contig_kernel   groups run along the contiguous axis (values: [.., T, D], groups over D;
-//                         or keys already transposed to [.., D, T]).  A thread owns one output
-//                         word; the threads of a group combine min/max with shuffles.
+//                         or keys already transposed to [.., D, T]).  A thread owns one or two output
+//                         words; the threads of a group combine min/max with shuffles.
 //   quant_strided_kernel  groups run along a strided axis while the *other* axis is contiguous
 //                         (keys left as [.., T, D], groups over T).  A thread owns two adjacent
 //                         channels, keeps a whole group in registers (all loads in flight at
@@ -31,19 +31,49 @@ __device__ __forceinline__ int round_code(float n, int emax) {
     return max(0, min(k, emax));
 }
 
-// Code of one element, bit-identical to clamp(roundf((v - lo) / sc), 0, emax) with IEEE division, without
-// paying for a division per element: y = (v - lo) * rinv with rinv = fl(1/sc) is within 3e-6 of the true
-// quotient, and so is the IEEE quotient; unless y lies within 1e-4 of a rounding boundary (k + 0.5) both
-// round to the same integer.  The rare boundary cases (and NaN from a constant group, 0 * inf) take the
-// exact division.
-__device__ __forceinline__ int quant_code(float v, float lo, float sc, float rinv, int emax) {
-    const float a = v - lo;
-    const float y = a * rinv;
-    int k = __float2int_rz(y);
-    const float d = y - (float)k;
-    if (!(fabsf(d - 0.5f) >= 1e-4f)) return round_code(a / sc, emax);   // near a tie, or NaN
-    k += (d >= 0.5f) ? 1 : 0;
-    return max(0, min(k, emax));
+// One packed word of E = fields_per_word(BITS) consecutive elements get(0..E-1) of a group with minimum lo, scale
+// sc and rinv = fl(1/sc), bit-identical to OR_i clamp(roundf((v_i - lo) / sc), 0, emax_i) << shift_i with IEEE
+// division -- without a division, an int conversion or a clamp per element:
+//   m  = fma(a, rinv, 1.5 * 2^23), a = v - lo     the addition rounds a*rinv to the nearest integer (low mantissa bits)
+//   yr = m - 1.5 * 2^23                          that integer as a float (exact)
+//   e  = fma(a, rinv, -yr)                       signed distance of a*rinv from it, in [-0.5, 0.5]
+// a*rinv and the IEEE quotient differ by < 1.3e-7 relative (< 2e-6 for codes up to 15), so unless |e| is within
+// 1e-5 of 0.5 both round to the same integer, whatever the tie rule; 0 <= a*rinv <= qmax (1 + 2e-7) keeps it in
+// range.  The word is summed in two fp32 chunks of <= 17 bits (exact) and converted once.  If any element is near
+// a tie or not finite (constant group: 0 * inf), the whole word is redone with the exact division.
+template <int BITS, typename Get>
+__device__ __forceinline__ uint32_t quant_word(Get get, float lo, float sc, float rinv) {
+    constexpr int E = fields_per_word(BITS);
+    constexpr int QMAX = (1 << BITS) - 1;
+    constexpr int NLO = (BITS == 3) ? 5 : E / 2;               // fields in the low chunk
+    constexpr int HI_SHIFT = (BITS == 3) ? 15 : BITS * NLO;
+    constexpr float kMagic = 12582912.0f;
+    float wl = 0.f, wh = 0.f;
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        const float a = get(i) - lo;
+        const float m = fmaf(a, rinv, kMagic);
+        float yr = m - kMagic;
+        const float e = fmaf(a, rinv, -yr);
+        ok = ok && (fabsf(e) <= 0.49999f);
+        if (BITS == 3 && i == 10) yr = fminf(yr, 3.f);          // the 11th code of a 3-bit group has two bits
+        if (i < NLO) {
+            wl = fmaf(yr, (float)(1 << (BITS * i)), wl);
+        } else {
+            const int sh = (BITS == 3) ? (i < 10 ? 3 * (i - 5) : 15) : BITS * (i - NLO);
+            wh = fmaf(yr, (float)(1 << sh), wh);
+        }
+    }
+    if (ok) return __float2uint_rz(wl) | (__float2uint_rz(wh) << HI_SHIFT);
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        const float n = (get(i) - lo) / sc;
+        if (BITS == 3) word |= (uint32_t)round_code(n, i < 10 ? 7 : 3) << (i < 10 ? 3 * i : 30);
+        else word |= (uint32_t)round_code(n, QMAX) << (BITS * i);
+    }
+    return word;
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
@@ -68,31 +98,34 @@ __device__ __forceinline__ float stored_scale(float range, float quotient, int b
 }
 
 // ---------------------------------------------------------------------------------------------
-// Contiguous groups.  E = fields per word elements per thread, TPG = group / E threads per group.
-template <int BITS, typename T>
+// Contiguous groups.  A thread owns WPT consecutive words (E * WPT elements, 32 where the shapes allow: 64 bytes
+// of loads in flight per thread, and the per-thread index arithmetic, division and shuffles spread over enough
+// elements); tpg = group / (E * WPT) threads share a group.
+template <int BITS, typename T, int WPT>
 __global__ void __launch_bounds__(256) quant_contig_kernel(const T *__restrict__ x, int32_t *__restrict__ code,
                                                            T *__restrict__ scale, T *__restrict__ mn, QuantDims d,
                                                            int tpg, bool vec_ok, bool linear) {
     constexpr int E = fields_per_word(BITS);
-    // blockIdx.y = (b, h); inside a (b, h) slab words are numbered linearly (32-bit index arithmetic)
-    const int words_per_row = (int)(d.S / E);
-    const int total = (int)d.A * words_per_row;
+    constexpr int EW = E * WPT;
+    // blockIdx.y = (b, h); inside a (b, h) slab units of WPT words are numbered linearly (32-bit index arithmetic)
+    const int units_per_row = (int)(d.S / EW);
+    const int total = (int)d.A * units_per_row;
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     const bool active = idx < total;
     if (!active) idx = total - 1;  // keep the lane alive for the shuffles
     const int b = blockIdx.y / (int)d.H, h = blockIdx.y % (int)d.H;
-    int a, w;
-    if (linear) { a = 0; w = idx; }                      // rows of the slab are back to back in x, code and scale
-    else { a = idx / words_per_row; w = idx - a * words_per_row; }
-    const T *px = x + b * d.x_sB + h * d.x_sH + a * d.x_sA + (int64_t)w * E;
+    int a, u;
+    if (linear) { a = 0; u = idx; }                      // rows of the slab are back to back in x, code and scale
+    else { a = idx / units_per_row; u = idx - a * units_per_row; }
+    const T *px = x + b * d.x_sB + h * d.x_sH + a * d.x_sA + (int64_t)u * EW;
 
-    float v[E];
-    if constexpr (sizeof(T) == 2 && (E % 8 == 0)) {
+    float v[EW];
+    if constexpr (sizeof(T) == 2 && (EW % 8 == 0)) {
         if (vec_ok) {
 #pragma unroll
-            for (int j = 0; j < E / 8; ++j) {
-                uint4 u = __ldg(reinterpret_cast<const uint4 *>(px) + j);
-                const __half2 *hp = reinterpret_cast<const __half2 *>(&u);
+            for (int j = 0; j < EW / 8; ++j) {
+                uint4 q = __ldg(reinterpret_cast<const uint4 *>(px) + j);
+                const __half2 *hp = reinterpret_cast<const __half2 *>(&q);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     float2 f = __half22float2(hp[k]);
@@ -102,36 +135,31 @@ __global__ void __launch_bounds__(256) quant_contig_kernel(const T *__restrict__
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < E; ++i) v[i] = to_f32<T>(px[i]);
+            for (int i = 0; i < EW; ++i) v[i] = to_f32<T>(px[i]);
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < E; ++i) v[i] = to_f32<T>(px[i]);
+        for (int i = 0; i < EW; ++i) v[i] = to_f32<T>(px[i]);
     }
     float lo = v[0], hi = v[0];
 #pragma unroll
-    for (int i = 1; i < E; ++i) { lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]); }
+    for (int i = 1; i < EW; ++i) { lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]); }
     for (int o = 1; o < tpg; o <<= 1) {
         lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
         hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
     }
     constexpr int QMAX = (1 << BITS) - 1;
     const float sc = (hi - lo) / (float)QMAX;
-    const float rinv = 1.0f / sc;
-    uint32_t word = 0;
+    const float rinv = __frcp_rn(sc);                          // correctly rounded 1 / sc
+    uint32_t word[WPT];
 #pragma unroll
-    for (int i = 0; i < E; ++i) {
-        if constexpr (BITS == 3) {
-            const int q = quant_code(v[i], lo, sc, rinv, i < 10 ? 7 : 3);
-            word |= (uint32_t)q << (i < 10 ? 3 * i : 30);
-        } else {
-            word |= (uint32_t)quant_code(v[i], lo, sc, rinv, QMAX) << (BITS * i);
-        }
-    }
+    for (int k = 0; k < WPT; ++k) word[k] = quant_word<BITS>([&](int i) { return v[k * E + i]; }, lo, sc, rinv);
     if (active) {
-        code[b * d.c_sB + h * d.c_sH + a * d.c_sA + w] = (int32_t)word;
-        if ((w & (tpg - 1)) == 0) {                           // tpg is a power of two
-            const int64_t zo = b * d.z_sB + h * d.z_sH + a * d.z_sA + (w >> (__ffs(tpg) - 1));
+        int32_t *pc = code + b * d.c_sB + h * d.c_sH + a * d.c_sA + u * WPT;
+#pragma unroll
+        for (int k = 0; k < WPT; ++k) pc[k] = (int32_t)word[k];
+        if ((u & (tpg - 1)) == 0) {                           // tpg is a power of two
+            const int64_t zo = b * d.z_sB + h * d.z_sH + a * d.z_sA + (u >> (__ffs(tpg) - 1));
             scale[zo] = from_f32<T>(stored_scale<QMAX>(hi - lo, sc, d.by_div));
             mn[zo] = from_f32<T>(lo);
         }
@@ -151,7 +179,7 @@ struct StridedCfg {
 };
 
 template <int BITS, int G>
-__global__ void __launch_bounds__(256) quant_strided_kernel(const __half *__restrict__ x, int32_t *__restrict__ code,
+__global__ void __launch_bounds__(256, 3) quant_strided_kernel(const __half *__restrict__ x, int32_t *__restrict__ code,
                                                             __half *__restrict__ scale, __half *__restrict__ mn,
                                                             QuantDims d) {
     using C = StridedCfg<BITS, G>;
@@ -187,7 +215,7 @@ __global__ void __launch_bounds__(256) quant_strided_kernel(const __half *__rest
             }
         }
         const float sc0 = (hi0 - lo0) / (float)QMAX, sc1 = (hi1 - lo1) / (float)QMAX;
-        const float ri0 = 1.0f / sc0, ri1 = 1.0f / sc1;
+        const float ri0 = __frcp_rn(sc0), ri1 = __frcp_rn(sc1);     // correctly rounded reciprocals
 #pragma unroll 1
         for (int c = 0; c < NCH; ++c) {
             if (NCH > 1) {                                    // long groups: second pass over the chunk (cache hit)
@@ -196,19 +224,8 @@ __global__ void __launch_bounds__(256) quant_strided_kernel(const __half *__rest
             }
 #pragma unroll
             for (int w = 0; w < WPCH; ++w) {
-                uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-                for (int i = 0; i < C::FPI; ++i) {
-                    const float2 f = __half22float2(raw[w * C::FPI + i]);
-                    if constexpr (BITS == 3) {
-                        const int em = i < 10 ? 7 : 3, sh = i < 10 ? 3 * i : 30;
-                        w0 |= (uint32_t)quant_code(f.x, lo0, sc0, ri0, em) << sh;
-                        w1 |= (uint32_t)quant_code(f.y, lo1, sc1, ri1, em) << sh;
-                    } else {
-                        w0 |= (uint32_t)quant_code(f.x, lo0, sc0, ri0, QMAX) << (BITS * i);
-                        w1 |= (uint32_t)quant_code(f.y, lo1, sc1, ri1, QMAX) << (BITS * i);
-                    }
-                }
+                const uint32_t w0 = quant_word<BITS>([&](int i) { return __low2float(raw[w * C::FPI + i]); }, lo0, sc0, ri0);
+                const uint32_t w1 = quant_word<BITS>([&](int i) { return __high2float(raw[w * C::FPI + i]); }, lo1, sc1, ri1);
                 s_code[(2 * pair) * C::WPAD + g * C::WPG + c * WPCH + w] = (int32_t)w0;
                 s_code[(2 * pair + 1) * C::WPAD + g * C::WPG + c * WPCH + w] = (int32_t)w1;
             }
@@ -291,16 +308,21 @@ static int launch_bits(const kvq_quant_args *a, const QuantDims &d, cudaStream_t
     if (total_words == 0) return KVQ_OK;
 
     // groups along the contiguous axis
-    const int tpg = G / E;
-    if (a->x_sS == 1 && G % E == 0 && tpg <= 32 && (tpg & (tpg - 1)) == 0) {
+    if (a->x_sS == 1 && G % E == 0) {
         bool vec_ok = sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && d.x_sB % 8 == 0 &&
                       d.x_sH % 8 == 0 && d.x_sA % 8 == 0;
-        const int64_t per_slab = d.A * (d.S / E);
-        if (per_slab < (1LL << 31) && d.B * d.H <= 65535) {
+        // 32 elements (64 B of fp16 in flight) per thread where the group and the row allow it: 4 / 2 words for 4 / 2 bits
+        constexpr int WMAX = (sizeof(T) == 2 && E < 32 && 32 % E == 0) ? 32 / E : 1;
+        const bool wide = WMAX > 1 && vec_ok && G % (WMAX * E) == 0 && (d.S / E) % WMAX == 0;
+        const int wpt = wide ? WMAX : 1;
+        const int tpg = G / (E * wpt);
+        const int64_t per_slab = d.A * (d.S / (E * wpt));
+        if (tpg <= 32 && (tpg & (tpg - 1)) == 0 && per_slab < (1LL << 31) && d.B * d.H <= 65535) {
             const int64_t wpr = d.S / E;
-            const bool linear = d.x_sA == d.S && d.c_sA == wpr && d.z_sA == wpr / tpg;
+            const bool linear = d.x_sA == d.S && d.c_sA == wpr && d.z_sA == d.S / G;
             dim3 grid((unsigned)((per_slab + 255) / 256), (unsigned)(d.B * d.H));
-            quant_contig_kernel<BITS, T><<<grid, 256, 0, st>>>(x, a->code, sc, mn, d, tpg, vec_ok, linear);
+            if (wide) quant_contig_kernel<BITS, T, WMAX><<<grid, 256, 0, st>>>(x, a->code, sc, mn, d, tpg, vec_ok, linear);
+            else quant_contig_kernel<BITS, T, 1><<<grid, 256, 0, st>>>(x, a->code, sc, mn, d, tpg, vec_ok, linear);
             return check_launch();
         }
     }
