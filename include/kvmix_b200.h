@@ -217,6 +217,16 @@ uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32_t T);
 int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream);
 
 /*
+ * How kvq_decode_attn would cut the token axis for B*nh query heads, T tokens and k_bits-bit keys (no upstream
+ * counterpart: upstream's GEMV never splits a row): *chunk tokens per split, *n_splits splits per head, the last
+ * one running to T.  tensor_core != 0 asks for the plan of the tensor-core kernel (aligned caches, see
+ * kvq_decode_attn), 0 for the generic kernel's.  Host-only; returns KVQ_OK or KVQ_ERR_NULL / KVQ_ERR_BITS /
+ * KVQ_ERR_SHAPE.
+ */
+int kvq_decode_attn_plan(int32_t B, int32_t nh, int32_t T, int32_t k_bits, int32_t tensor_core, int32_t *chunk,
+                         int32_t *n_splits);
+
+/*
  * kvq_decode_attn for callers that have no device memory to give.  (No counterpart in upstream KVmix:
  * there every call allocates through torch.)
  *

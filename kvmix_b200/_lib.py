@@ -85,6 +85,8 @@ def lib():
         L.kvq_decode_attn.argtypes = [C.POINTER(AttnArgs), vp]
         L.kvq_decode_attn_static.restype = C.c_int
         L.kvq_decode_attn_static.argtypes = [C.POINTER(AttnArgs), vp]
+        L.kvq_decode_attn_plan.restype = C.c_int
+        L.kvq_decode_attn_plan.argtypes = [i32, i32, i32, i32, i32, C.POINTER(i32), C.POINTER(i32)]
         L.kvq_decode_attn_workspace_bytes.restype = u64
         L.kvq_decode_attn_workspace_bytes.argtypes = [i32, i32, i32]
         _lib = L
@@ -93,7 +95,7 @@ def lib():
 
 EXPORTS = ["kvq_version", "kvq_error_string", "kvq_last_cuda_error", "kvq_features_per_int",
            "kvq_quant_lastdim", "kvq_append_kv", "kvq_gemv", "kvq_decode_attn", "kvq_decode_attn_workspace_bytes",
-           "kvq_decode_attn_static"]
+           "kvq_decode_attn_static", "kvq_decode_attn_plan"]
 
 
 def check(rc):

@@ -357,6 +357,18 @@ extern "C" uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32
     return (bytes + 255) / 256 * 256;
 }
 
+extern "C" int kvq_decode_attn_plan(int32_t B, int32_t nh, int32_t T, int32_t k_bits, int32_t tensor_core,
+                                    int32_t *chunk, int32_t *n_splits) {
+    using namespace kvq;
+    if (!chunk || !n_splits) return KVQ_ERR_NULL;
+    if (k_bits < 1 || k_bits > 4) return KVQ_ERR_BITS;
+    if (B <= 0 || nh <= 0 || T <= 0) return KVQ_ERR_SHAPE;
+    const SplitPlan p = plan_splits(T, k_bits, (int64_t)B * nh, tensor_core != 0);
+    *chunk = p.chunk;
+    *n_splits = p.n_splits;
+    return KVQ_OK;
+}
+
 extern "C" int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream) {
     using namespace kvq;
     if (!a) return KVQ_ERR_NULL;

@@ -3,6 +3,8 @@ import ctypes
 import os
 import re
 
+import pytest
+
 from kvmix_b200 import _lib
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -76,3 +78,44 @@ def test_argument_errors_need_no_gpu():
     t = _lib.AttnArgs()
     t.D = 64
     assert L.kvq_decode_attn(ctypes.byref(t), None) == -11
+
+
+def _plan(B, nh, T, kb, tc):
+    import ctypes
+    c, n = ctypes.c_int32(), ctypes.c_int32()
+    assert _lib.lib().kvq_decode_attn_plan(B, nh, T, kb, tc, ctypes.byref(c), ctypes.byref(n)) == 0
+    return c.value, n.value
+
+
+def test_split_plan_invariants_and_workspace_bound():
+    """Host-only: every plan covers T with its last split running to T, respects the score buffer of its kernel, and
+    never needs more workspace than kvq_decode_attn_workspace_bytes promises for any shorter context (a cache sizes
+    its workspace once, for its maximum length)."""
+    L = _lib.lib()
+    for B, nh in [(1, 1), (1, 32), (3, 8), (8, 32), (16, 32), (64, 32), (256, 32)]:
+        for Tmax in (1, 31, 352, 1024, 4096, 4119, 9000, 32768, 131072 + 300):
+            ws = L.kvq_decode_attn_workspace_bytes(B, nh, Tmax)
+            for T in sorted({1, Tmax // 3 + 1, Tmax - 1 if Tmax > 1 else 1, Tmax}):
+                for kb in (1, 2, 3, 4):
+                    for tc in (0, 1):
+                        chunk, n = _plan(B, nh, T, kb, tc)
+                        assert chunk > 0 and n >= 1
+                        assert (n - 1) * chunk < T
+                        last = T - (n - 1) * chunk
+                        unit = (352 if kb == 3 else 1024) if tc else (352 if kb == 3 else 128)
+                        assert chunk % unit == 0
+                        if tc:
+                            assert last <= (8096 if kb == 3 else 8192) + unit // 4 and chunk <= 8192
+                        else:
+                            assert last <= chunk <= 4224
+                        heads = B * nh
+                        need = 0 if n == 1 else ((heads * 4 + 255) // 256) * 256 + heads * n * 130 * 4
+                        assert need <= ws, (B, nh, Tmax, T, kb, tc, chunk, n)
+
+
+def test_split_plan_prefers_one_split_for_full_grids():
+    assert _plan(64, 32, 4119, 2, 1) == (4096, 1)          # the last split absorbs the 23-token remainder
+    assert _plan(64, 32, 4119, 3, 1)[1] == 1
+    assert _plan(1, 32, 131072, 4, 1)[1] > 8               # one long sequence: many splits
+    with pytest.raises(Exception):
+        _lib.check(_lib.lib().kvq_decode_attn_plan(1, 1, 16, 5, 1, None, None))
