@@ -202,18 +202,18 @@ __global__ void __launch_bounds__(256, 3) quant_strided_kernel(const __half *__r
     for (int g = slot; g < groups_here; g += 4) {
         const __half *pg = px + (g0 + g) * G * d.x_sS;
         __half2 raw[CH];
-        float lo0 = 3.402823466e+38f, hi0 = -3.402823466e+38f, lo1 = lo0, hi1 = hi0;
+        // min / max of the two channels in fp16x2 (exact: the data are fp16; NaN operands are skipped as by fminf)
+        __half2 lo2 = __floats2half2_rn(65504.f, 65504.f), hi2 = __floats2half2_rn(-65504.f, -65504.f);
+        bool first = true;
 #pragma unroll 1
         for (int c = 0; c < NCH; ++c) {
 #pragma unroll
             for (int i = 0; i < CH; ++i) raw[i] = __ldg(reinterpret_cast<const __half2 *>(pg + (int64_t)(c * CH + i) * d.x_sS));
+            if (first) { lo2 = raw[0]; hi2 = raw[0]; first = false; }
 #pragma unroll
-            for (int i = 0; i < CH; ++i) {
-                const float2 f = __half22float2(raw[i]);
-                lo0 = fminf(lo0, f.x); hi0 = fmaxf(hi0, f.x);
-                lo1 = fminf(lo1, f.y); hi1 = fmaxf(hi1, f.y);
-            }
+            for (int i = 0; i < CH; ++i) { lo2 = __hmin2(lo2, raw[i]); hi2 = __hmax2(hi2, raw[i]); }
         }
+        const float lo0 = __low2float(lo2), lo1 = __high2float(lo2), hi0 = __low2float(hi2), hi1 = __high2float(hi2);
         const float sc0 = (hi0 - lo0) / (float)QMAX, sc1 = (hi1 - lo1) / (float)QMAX;
         const float ri0 = __frcp_rn(sc0), ri1 = __frcp_rn(sc1);     // correctly rounded reciprocals
 #pragma unroll 1
@@ -238,15 +238,27 @@ __global__ void __launch_bounds__(256, 3) quant_strided_kernel(const __half *__r
     __syncthreads();
     const int words_here = groups_here * C::WPG;
     int32_t *pc = code + b * d.c_sB + h * d.c_sH + a0 * d.c_sA + g0 * C::WPG;
-    for (int i = threadIdx.x; i < 128 * words_here; i += 256) {
-        const int ch = i / words_here, w = i % words_here;
-        pc[ch * d.c_sA + w] = s_code[ch * C::WPAD + w];
-    }
     const int64_t zo = b * d.z_sB + h * d.z_sH + a0 * d.z_sA + g0;
-    for (int i = threadIdx.x; i < 128 * groups_here; i += 256) {
-        const int ch = i / groups_here, g = i % groups_here;
-        scale[zo + ch * d.z_sA + g] = s_scale[ch * (C::GPC + 2) + g];
-        mn[zo + ch * d.z_sA + g] = s_mn[ch * (C::GPC + 2) + g];
+    if (groups_here == C::GPC) {                              // full CTA: row lengths are compile-time constants
+        for (int i = threadIdx.x; i < 128 * C::WPC; i += 256) {
+            const int ch = i / C::WPC, w = i % C::WPC;
+            pc[ch * d.c_sA + w] = s_code[ch * C::WPAD + w];
+        }
+        for (int i = threadIdx.x; i < 128 * C::GPC; i += 256) {
+            const int ch = i / C::GPC, g = i % C::GPC;
+            scale[zo + ch * d.z_sA + g] = s_scale[ch * (C::GPC + 2) + g];
+            mn[zo + ch * d.z_sA + g] = s_mn[ch * (C::GPC + 2) + g];
+        }
+    } else {
+        for (int i = threadIdx.x; i < 128 * words_here; i += 256) {
+            const int ch = i / words_here, w = i % words_here;
+            pc[ch * d.c_sA + w] = s_code[ch * C::WPAD + w];
+        }
+        for (int i = threadIdx.x; i < 128 * groups_here; i += 256) {
+            const int ch = i / groups_here, g = i % groups_here;
+            scale[zo + ch * d.z_sA + g] = s_scale[ch * (C::GPC + 2) + g];
+            mn[zo + ch * d.z_sA + g] = s_mn[ch * (C::GPC + 2) + g];
+        }
     }
 }
 
