@@ -230,17 +230,23 @@ def main():
 
     def step_e2e():
         """One step through the public cache API with HOST inputs and outputs: each layer's q/k/v come from
-        pinned host memory (copy stream, overlapped with the previous layer's attention) and each layer's
-        output goes back to pinned host memory; the step ends when the last output has landed."""
+        pinned host memory (copy stream, issued one layer ahead and overlapped with the previous layer's
+        attention) and each layer's output goes back to pinned host memory; the step ends when the last output
+        has landed."""
         cur = torch.cuda.current_stream()
         s_in.wait_stream(cur)
-        with torch.cuda.stream(s_in):
-            for l in range(L):
+
+        def copy_in(l):                                # layer l's inputs, one layer ahead of its kernels
+            with torch.cuda.stream(s_in):
                 dq[l].copy_(hq[l], non_blocking=True)
                 dk[l].copy_(hk[l], non_blocking=True)
                 dv[l].copy_(hv[l], non_blocking=True)
                 ev_in[l].record(s_in)
+
+        copy_in(0)
         for l in range(L):
+            if l + 1 < L:
+                copy_in(l + 1)
             cur.wait_event(ev_in[l])
             caches[l].decode_step(dq[l], dk[l], dv[l], out=dout[l])
             if head_sharded:
