@@ -164,6 +164,11 @@ int kvq_gemv(const kvq_gemv_args *a, kvq_stream_t stream);
  *   vcode  [B, nh_kv, Tvq, D/fpi_v]     strides vc_sB, vc_sH, vc_sT (words)
  *   vscale, vmn [B, nh_kv, Tvq, D/v_group] fp16, strides vs_sB, vs_sH, vs_sT
  *   vfull  [B, nh_kv, vf_cap, D] fp16   strides vf_sB, vf_sH, vf_sT, ring like kfull
+ * Two kernels serve the call.  The tensor-core kernel takes D = 128, k_group in {32, 64, 128} (11 for 3-bit keys),
+ * v_group in {32, 64, 128}, Tvq a multiple of 32, nh a multiple of nh_kv, every packed tensor and fp16 tail 16-byte
+ * aligned with row strides that keep rows 16-byte aligned (kc_sD % 4, ks_sD % 8, kf_sT % 8, vf_sT % 8 == 0; value
+ * rows contiguous: vc_sT == D/fpi_v, vs_sT == D/v_group) -- what a preallocated cache provides.  Anything else runs
+ * on a slower CUDA-core kernel with the same results.
  * D must be 128.  k_group and v_group must be multiples of the fields per word (k_group == 11 for
  * 3-bit keys); 3-bit values need D % 11 == 0 upstream and are rejected here for D = 128.
  * round_scores != 0 narrows each raw score to fp16 before scaling, as upstream's GEMV and fp16

@@ -996,8 +996,8 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
 }
 
 // ---------------------------------------------------------------------------------------------
-// The tensor-core path needs one query head per kv head, supported group sizes, 16-byte aligned and
-// row-contiguous packed tensors (cp.async granules), and a packed-value length that is a multiple of 16.
+// The tensor-core path needs a whole number of query heads per kv head, supported group sizes, 16-byte aligned
+// and row-contiguous packed tensors (cp.async granules), and a packed-value length that is a multiple of 32.
 bool mma_path_eligible(const kvq_attn_args &a) {
     if (a.nh_kv <= 0 || a.nh % a.nh_kv != 0 || a.D != kHeadDim) return false;
     if (a.k_bits == 3) {
