@@ -93,6 +93,42 @@ typedef struct {
 int kvq_quant_lastdim(const kvq_quant_args *a, kvq_stream_t stream);
 
 /*
+ * The functional append forms: out = previous ++ quantize(x), written into caller-allocated contiguous tensors.
+ * Replace process_key_quantization_cuda (upstream quant_cuda/csrc/quantization_cuda.cu:298-411) and
+ * process_value_quantization_cuda (:413-537), whose wrappers allocate the outputs and whose kernels copy the
+ * previous tensors and quantize the new tokens.  (A preallocated cache does not need them: it points
+ * kvq_quant_lastdim at its first free word and moves nothing.)
+ *
+ * kvq_append_k: x [B,H,D,Tn] (strides x_sB, x_sH, x_sA, x_sS over those four axes), groups over the Tn new tokens;
+ *   prev_code [B,H,D,old_words], prev_scale/prev_mn [B,H,D,old_groups] contiguous (NULL when old_* == 0);
+ *   code [B,H,D,old_words + Tn/fpi], scale/mn [B,H,D,old_groups + Tn/group] contiguous.
+ * kvq_append_v: x [B,H,Tn,D] (same four strides), groups over D; old_tokens previous tokens:
+ *   prev_code [B,H,old_tokens,D/fpi], prev_scale/prev_mn [B,H,old_tokens,D/group] contiguous;
+ *   code [B,H,old_tokens+Tn,D/fpi], scale/mn [B,H,old_tokens+Tn,D/group] contiguous.
+ * The stored scale is the quotient (max-min)/(2^b-1), as the upstream append kernels store it (:51-53, :232-234).
+ * Previous 3-bit code words are copied as well (upstream's fused 3-bit key kernel leaves them uninitialised,
+ * :131-134).  Same divisibility rules and error codes as kvq_quant_lastdim.
+ */
+typedef struct {
+    const void *x;
+    int32_t x_is_f32;
+    int64_t B, H, A, S;                 /* x is [B,H,A,S]: keys A = D, S = Tn; values A = Tn, S = D */
+    int64_t x_sB, x_sH, x_sA, x_sS;
+    int32_t group, bits;
+    const int32_t *prev_code;
+    const void *prev_scale;
+    const void *prev_mn;
+    int64_t old_words, old_groups;      /* kvq_append_k: previous words / groups per channel row */
+    int64_t old_tokens;                 /* kvq_append_v: previous tokens */
+    int32_t *code;
+    void *scale;
+    void *mn;
+} kvq_append_form_args;
+
+int kvq_append_k(const kvq_append_form_args *a, kvq_stream_t stream);
+int kvq_append_v(const kvq_append_form_args *a, kvq_stream_t stream);
+
+/*
  * Append one token's keys and values (fp16, after RoPE) to the fp16 tails of the cache, in one launch.
  * Replaces the two torch.cat calls upstream makes per layer and step (models/modeling_llama_KVmix.py:111-112)
  * without moving the old tail: row `k_slot` of kfull and row `v_slot` of vfull are overwritten.

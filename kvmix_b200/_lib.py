@@ -38,6 +38,14 @@ class AppendArgs(C.Structure):
                 ("vfull", vp), ("vf_sB", i64), ("vf_sH", i64), ("vf_sT", i64), ("v_slot", i32)]
 
 
+class AppendFormArgs(C.Structure):
+    _fields_ = [("x", vp), ("x_is_f32", i32), ("B", i64), ("H", i64), ("A", i64), ("S", i64),
+                ("x_sB", i64), ("x_sH", i64), ("x_sA", i64), ("x_sS", i64), ("group", i32), ("bits", i32),
+                ("prev_code", vp), ("prev_scale", vp), ("prev_mn", vp),
+                ("old_words", i64), ("old_groups", i64), ("old_tokens", i64),
+                ("code", vp), ("scale", vp), ("mn", vp)]
+
+
 class AttnArgs(C.Structure):
     _fields_ = [("B", i32), ("nh", i32), ("nh_kv", i32), ("D", i32),
                 ("T", i32), ("Tkq", i32), ("Tvq", i32),
@@ -85,6 +93,9 @@ def lib():
         L.kvq_decode_attn.argtypes = [C.POINTER(AttnArgs), vp]
         L.kvq_decode_attn_static.restype = C.c_int
         L.kvq_decode_attn_static.argtypes = [C.POINTER(AttnArgs), vp]
+        for fn in (L.kvq_append_k, L.kvq_append_v):
+            fn.restype = C.c_int
+            fn.argtypes = [C.POINTER(AppendFormArgs), vp]
         L.kvq_decode_attn_plan.restype = C.c_int
         L.kvq_decode_attn_plan.argtypes = [i32, i32, i32, i32, i32, C.POINTER(i32), C.POINTER(i32)]
         L.kvq_decode_attn_workspace_bytes.restype = u64
@@ -95,7 +106,7 @@ def lib():
 
 EXPORTS = ["kvq_version", "kvq_error_string", "kvq_last_cuda_error", "kvq_features_per_int",
            "kvq_quant_lastdim", "kvq_append_kv", "kvq_gemv", "kvq_decode_attn", "kvq_decode_attn_workspace_bytes",
-           "kvq_decode_attn_static", "kvq_decode_attn_plan"]
+           "kvq_decode_attn_static", "kvq_decode_attn_plan", "kvq_append_k", "kvq_append_v"]
 
 
 def check(rc):

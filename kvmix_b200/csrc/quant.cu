@@ -400,3 +400,82 @@ extern "C" int kvq_quant_lastdim(const kvq_quant_args *a, kvq_stream_t stream) {
 #undef KVQ_DISPATCH
     return KVQ_ERR_BITS;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Functional append forms: copy the previous tensors into the front of the outputs (strided device-to-device
+// copies on the same stream), then quantize the new tokens in place behind them.
+namespace kvq {
+static int copy_rows(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width, size_t rows,
+                     cudaStream_t st) {
+    if (width == 0 || rows == 0) return KVQ_OK;
+    if (!src || !dst) return KVQ_ERR_NULL;
+    return record_cuda_error(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width, rows, cudaMemcpyDeviceToDevice, st));
+}
+}  // namespace kvq
+
+extern "C" int kvq_append_k(const kvq_append_form_args *a, kvq_stream_t stream) {
+    using namespace kvq;
+    if (!a) return KVQ_ERR_NULL;
+    if (a->bits < 1 || a->bits > 4) return KVQ_ERR_BITS;
+    if (a->B < 0 || a->H < 0 || a->A < 0 || a->S < 0 || a->old_words < 0 || a->old_groups < 0) return KVQ_ERR_SHAPE;
+    if (a->bits == 3 && a->group != 11) return KVQ_ERR_GROUP3;
+    if (a->group <= 0) return KVQ_ERR_DIVGROUP;
+    if (a->bits == 3) {
+        if (a->S % 11 != 0) return KVQ_ERR_DIV11;
+    } else {
+        if (a->S % a->group != 0) return KVQ_ERR_DIVGROUP;
+        if (a->S % (32 / a->bits) != 0) return KVQ_ERR_DIVWORD;
+    }
+    const int fpi = fields_per_word(a->bits);
+    const int64_t new_words = a->S / fpi, new_groups = a->S / a->group;
+    const int64_t rows = a->B * a->H * a->A, W = a->old_words + new_words, Gn = a->old_groups + new_groups;
+    const size_t es = a->x_is_f32 ? 4 : 2;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int rc = copy_rows(a->code, (size_t)W * 4, a->prev_code, (size_t)a->old_words * 4, (size_t)a->old_words * 4, (size_t)rows, st);
+    if (rc) return rc;
+    rc = copy_rows(a->scale, (size_t)Gn * es, a->prev_scale, (size_t)a->old_groups * es, (size_t)a->old_groups * es, (size_t)rows, st);
+    if (rc) return rc;
+    rc = copy_rows(a->mn, (size_t)Gn * es, a->prev_mn, (size_t)a->old_groups * es, (size_t)a->old_groups * es, (size_t)rows, st);
+    if (rc) return rc;
+    kvq_quant_args q{a->x, a->x_is_f32, a->B, a->H, a->A, a->S, a->x_sB, a->x_sH, a->x_sA, a->x_sS, a->group, a->bits, 1,
+                     a->code ? a->code + a->old_words : nullptr, a->H * a->A * W, a->A * W, W,
+                     a->scale ? static_cast<char *>(a->scale) + (size_t)a->old_groups * es : nullptr,
+                     a->mn ? static_cast<char *>(a->mn) + (size_t)a->old_groups * es : nullptr,
+                     a->H * a->A * Gn, a->A * Gn, Gn};
+    return kvq_quant_lastdim(&q, stream);
+}
+
+extern "C" int kvq_append_v(const kvq_append_form_args *a, kvq_stream_t stream) {
+    using namespace kvq;
+    if (!a) return KVQ_ERR_NULL;
+    if (a->bits < 1 || a->bits > 4) return KVQ_ERR_BITS;
+    if (a->B < 0 || a->H < 0 || a->A < 0 || a->S < 0 || a->old_tokens < 0) return KVQ_ERR_SHAPE;
+    if (a->bits == 3 && a->group != 11) return KVQ_ERR_GROUP3;
+    if (a->group <= 0) return KVQ_ERR_DIVGROUP;
+    if (a->bits == 3) {
+        if (a->S % 11 != 0) return KVQ_ERR_DIV11;
+    } else {
+        if (a->S % a->group != 0) return KVQ_ERR_DIVGROUP;
+        if (a->S % (32 / a->bits) != 0) return KVQ_ERR_DIVWORD;
+    }
+    const int fpi = fields_per_word(a->bits);
+    const int64_t wpt = a->S / fpi, gpt = a->S / a->group;           // words / groups per token row
+    const int64_t rows = a->B * a->H, Tt = a->old_tokens + a->A;
+    const size_t es = a->x_is_f32 ? 4 : 2;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int rc = copy_rows(a->code, (size_t)(Tt * wpt) * 4, a->prev_code, (size_t)(a->old_tokens * wpt) * 4,
+                       (size_t)(a->old_tokens * wpt) * 4, (size_t)rows, st);
+    if (rc) return rc;
+    rc = copy_rows(a->scale, (size_t)(Tt * gpt) * es, a->prev_scale, (size_t)(a->old_tokens * gpt) * es,
+                   (size_t)(a->old_tokens * gpt) * es, (size_t)rows, st);
+    if (rc) return rc;
+    rc = copy_rows(a->mn, (size_t)(Tt * gpt) * es, a->prev_mn, (size_t)(a->old_tokens * gpt) * es,
+                   (size_t)(a->old_tokens * gpt) * es, (size_t)rows, st);
+    if (rc) return rc;
+    kvq_quant_args q{a->x, a->x_is_f32, a->B, a->H, a->A, a->S, a->x_sB, a->x_sH, a->x_sA, a->x_sS, a->group, a->bits, 1,
+                     a->code ? a->code + a->old_tokens * wpt : nullptr, a->H * Tt * wpt, Tt * wpt, wpt,
+                     a->scale ? static_cast<char *>(a->scale) + (size_t)(a->old_tokens * gpt) * es : nullptr,
+                     a->mn ? static_cast<char *>(a->mn) + (size_t)(a->old_tokens * gpt) * es : nullptr,
+                     a->H * Tt * gpt, Tt * gpt, gpt};
+    return kvq_quant_lastdim(&q, stream);
+}

@@ -18,7 +18,7 @@ import math
 import torch
 
 from . import _lib
-from ._lib import AttnArgs, GemvArgs, QuantArgs, check
+from ._lib import AppendFormArgs, AttnArgs, GemvArgs, QuantArgs, check
 
 
 LAUNCHES = [0]     # kernels of this library launched through this module (benchmark bookkeeping)
@@ -169,16 +169,17 @@ def process_key_quantization_cuda(input_tensor, previous_code, previous_scale, p
     elif Tn % group_length != 0:
         raise RuntimeError("new_steps must be divisible by group_length")
     fpi = features_per_int(quant_bits)
+    previous_code, previous_scale, previous_min = (t.contiguous() for t in (previous_code, previous_scale, previous_min))
     old_w, old_g = previous_code.shape[3], previous_scale.shape[3]
     dev, dt = input_tensor.device, input_tensor.dtype
     code = torch.empty((B, H, D, old_w + Tn // fpi), dtype=torch.int32, device=dev)
     scale = torch.empty((B, H, D, old_g + Tn // group_length), dtype=dt, device=dev)
     mn = torch.empty_like(scale)
-    code[..., :old_w].copy_(previous_code)
-    scale[..., :old_g].copy_(previous_scale)
-    mn[..., :old_g].copy_(previous_min)
-    quantize_into(input_tensor, group_length, quant_bits, code[..., old_w:], scale[..., old_g:], mn[..., old_g:],
-                  scale_by_division=True)
+    a = AppendFormArgs(input_tensor.data_ptr(), int(dt == torch.float32), B, H, D, Tn, *input_tensor.stride(),
+                       group_length, quant_bits, previous_code.data_ptr(), previous_scale.data_ptr(),
+                       previous_min.data_ptr(), old_w, old_g, 0, code.data_ptr(), scale.data_ptr(), mn.data_ptr())
+    check(_lib.lib().kvq_append_k(C.byref(a), _stream()))
+    LAUNCHES[0] += 1
     return code, scale, mn
 
 
@@ -198,16 +199,17 @@ def process_value_quantization_cuda(input_tensor, previous_code, previous_scale,
     elif D % group_length != 0:
         raise RuntimeError("head_dim must be divisible by group_length")
     fpi = features_per_int(quant_bits)
+    previous_code, previous_scale, previous_min = (t.contiguous() for t in (previous_code, previous_scale, previous_min))
     Told = previous_code.shape[2]
     dev, dt = input_tensor.device, input_tensor.dtype
     code = torch.empty((B, H, Told + Tn, D // fpi), dtype=torch.int32, device=dev)
     scale = torch.empty((B, H, Told + Tn, D // group_length), dtype=dt, device=dev)
     mn = torch.empty_like(scale)
-    code[:, :, :Told].copy_(previous_code)
-    scale[:, :, :Told].copy_(previous_scale)
-    mn[:, :, :Told].copy_(previous_min)
-    quantize_into(input_tensor, group_length, quant_bits, code[:, :, Told:], scale[:, :, Told:], mn[:, :, Told:],
-                  scale_by_division=True)
+    a = AppendFormArgs(input_tensor.data_ptr(), int(dt == torch.float32), B, H, Tn, D, *input_tensor.stride(),
+                       group_length, quant_bits, previous_code.data_ptr(), previous_scale.data_ptr(),
+                       previous_min.data_ptr(), 0, 0, Told, code.data_ptr(), scale.data_ptr(), mn.data_ptr())
+    check(_lib.lib().kvq_append_v(C.byref(a), _stream()))
+    LAUNCHES[0] += 1
     return code, scale, mn
 
 

@@ -28,6 +28,11 @@ def _layer(cuda, B, hkv, T, kb, vb, G, window, extra=8):
     return c, k, v
 
 
+def _query(cuda, B, nh, seed):
+    g = torch.Generator(device=cuda).manual_seed(seed)
+    return torch.randn((B, nh, 1, 128), generator=g, device=cuda, dtype=torch.float16)
+
+
 def _ref_for_sequence(k, v, b, kb, vb, G, window):
     ref = RefLayerCache(kb, vb, G, residual_length=window)
     ref.prefill(k[b:b + 1].cpu().numpy(), v[b:b + 1].cpu().numpy())
@@ -55,7 +60,7 @@ def test_config2_layer_full_batch(cuda):
     """Llama-2-7B geometry: batch 64, 32 heads (MHA), context 4096, K3V2 (group 11 / 32), window 128."""
     B, H, T = 64, 32, 4096
     c, k, v = _layer(cuda, B, H, T, 3, 2, 32, 128)
-    q = torch.randn((B, H, 1, 128), device=cuda, dtype=torch.float16)
+    q = _query(cuda, B, H, 102)
     _check_one_sequence(cuda, c, k, v, q, 5, 3, 2, 32, 128)
     # a sequence's output does not depend on the rest of the batch
     full = c.attend(q)
@@ -70,7 +75,7 @@ def test_config3_layer_gqa_long_context(cuda, kb, vb):
     """Mistral-7B geometry: batch 8, 32 query / 8 KV heads, context 32768, group 64, window 128."""
     B, nh, hkv, T = 8, 32, 8, 32768
     c, k, v = _layer(cuda, B, hkv, T, kb, vb, 64, 128)
-    q = torch.randn((B, nh, 1, 128), device=cuda, dtype=torch.float16)
+    q = _query(cuda, B, nh, 103)
     _check_one_sequence(cuda, c, k, v, q, 3, kb, vb, 64, 128)
 
 
@@ -80,7 +85,7 @@ def test_config5_layer_131k_tokens_and_head_sharding(cuda):
     from kvmix_b200 import sharding
     B, nh, hkv, T = 1, 32, 8, 131072
     c, k, v = _layer(cuda, B, hkv, T, 3, 2, 128, 256)
-    q = torch.randn((B, nh, 1, 128), device=cuda, dtype=torch.float16)
+    q = _query(cuda, B, nh, 105)
     _check_one_sequence(cuda, c, k, v, q, 0, 3, 2, 128, 256)
     full = c.attend(q)
     parts = []
