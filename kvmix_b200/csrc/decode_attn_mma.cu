@@ -13,8 +13,9 @@
 //
 // Keys (codes [D, T/fpi], one word = fpi tokens of one channel; scale/zero [D, T/G]):
 //   A (16x16) = codes, rows = tokens, cols = 16 channels.  q[d]*scale[d,g] is carried as an exact fp16 pair hi + lo.
-//   A warp tile (256 tokens; 88 for 3-bit keys) is worked as two halves whose MMA rows touch at most four groups,
-//   so B (16x8) holds {hi, lo} x 4 groups side by side and one MMA per code tile yields both parts.  The zero term
+//   A 256-token warp tile is worked as two halves whose MMA rows touch at most four groups, so B (16x8) holds
+//   {hi, lo} x 4 groups side by side and one MMA per code tile yields both parts.  3-bit keys (88-token tiles, every
+//   word its own group of 11) multiply each code tile by the hi and by the lo operand instead.  The zero term
 //   sum_d q[d]*zero[d,g] (hi and lo) is summed over channels by MMAs whose A operand is all ones.
 // Values (codes [T, D/fpi], one word = fpi channels of one token; scale/zero [T, D/G]):
 //   A (16x16) = codes, rows = channels, cols = 16 tokens;  B (16x8): column 2j = p[t]*scale[t,j], column 2j+1 =
@@ -162,21 +163,6 @@ template <> struct VFields<1> {
     }
 };
 
-// Every other 3-bit field of two words (already shifted right by 3 for the odd fields): r[i] = fp16x2 of the
-// fields at bits 6i of wa (low half) and wb (high half), left at bit position {0, 6, 6, 2, 8, 8}[i] of its half
-// (patterns below 2^11 are linear in fp16: subnormals and the first normal binade).  The field at bit 30 holds two
-// bits (the 11th code of a group) or, in the shifted words, nothing.
-__device__ __forceinline__ void unpack3_alternate(uint32_t wa, uint32_t wb, uint32_t (&r)[6]) {
-    const uint32_t x = prmt(wa, wb, 0x5410), y = prmt(wa, wb, 0x7632);
-    const uint32_t x1 = x >> 6, y1 = y >> 6;
-    r[0] = x & 0x00070007u;      // bits  0.. 2
-    r[1] = x & 0x01c001c0u;      // bits  6.. 8
-    r[2] = x1 & 0x01c001c0u;     // bits 12..14 -> 6..8
-    r[3] = y & 0x001c001cu;      // bits 18..20 -> 2..4 of the high half-word
-    r[4] = y & 0x07000700u;      // bits 24..26 -> 8..10
-    r[5] = y1 & 0x03000300u;     // bits 30..31 -> 8..9
-}
-
 // ---------------------------------------------------------------------------------------------
 // Key-side geometry per bit width.  A warp tile is 8 lane-octets x TPO tokens; code words reach the
 // warp through its own ring of cp.async stages in shared memory (padded rows so the fragment loads
@@ -319,14 +305,12 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     const uint32_t sz_s = ring_s + G::NS * G::STAGE_BYTES;                    // [2][128][8] halfs
     const int gr = lane % G::GPR, row0 = lane / G::GPR;
     const uint32_t cp_dst = ring_s + row0 * G::RS + gr * 16;                   // + slot*STAGE + i*RPI*RS
-    // The tile is worked as two halves, so that the 16 rows of one MMA touch at most four groups and the eight B
-    // columns can carry {hi, lo} of q*scale for those four side by side.  1/2/4-bit: octet g owns tokens
-    // [128 h + 16 g, +16) of half h.  3-bit (a word = 11 tokens = one group): octets g and g+4 share word 4h + (g & 3)
-    // of half h, the lower octet taking its even fields (0,2,..,10), the upper one its odd fields (1,3,..,9).
+    // 3-bit: octet g owns the word of group g (11 tokens).  Other widths: the tile is worked as two halves of 128
+    // tokens, octet g owning tokens [128 h + 16 g, +16) of half h, so that the 16 rows of one MMA touch at most four
+    // groups and the eight B columns can carry {hi, lo} of q*scale for those four side by side.
     constexpr int HW = (KB == 4) ? 2 : 1;                                      // code words per octet per half
-    const uint32_t frag_s = ring_s + (2 * tig) * G::RS +
-                            ((KB == 4) ? 8 * g : (KB == 2) ? 4 * g : (KB == 1) ? 4 * (g >> 1) : 4 * (g & 3));
-    const int sh3 = (g >= 4) ? 3 : 0;                                          // 3-bit: odd fields move to the even positions
+    const uint32_t frag_s = (KB == 3) ? ring_s + (2 * tig) * G::RS + g * 4
+                                      : ring_s + (2 * tig) * G::RS + ((KB == 4) ? 8 * g : (KB == 2) ? 4 * g : 4 * (g >> 1));
     const int wshift = (KB == 1) ? 16 * (g & 1) : 0;
     // ldmatrix.x4 row addresses: lanes 0-7 scale rows 16ksx+0..7, 8-15 scale rows +8..15, 16-31 the same of the zero tile
     const uint32_t ldm_s = sz_s + (((lane >> 3) & 1) * 8 + (lane & 7)) * 16 + (lane >> 4) * 2048;
@@ -391,8 +375,9 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
         // q*scale needs 22 bits; it is carried as an fp16 pair hi + lo (lo = fma(q, s, -hi) is exact), so the key
         // side adds no rounding beyond the fp32 accumulation.  The zero term gets the same treatment and is summed
         // over channels by MMAs whose A operand is all ones (one accumulator per half of the pair: short chains).
-        // b0 / b1 serve the first / second half of the tile; column n carries group (n / 2) of that half, hi in even
-        // and lo in odd columns, so one MMA per code tile yields both parts.
+        // 3-bit keys: b0 = hi and b1 = lo of the eight groups of the tile, every code tile is multiplied by both.
+        // Other widths: b0 / b1 serve the first / second half of the tile; column n carries group (n / 2) of that
+        // half, hi in even and lo in odd columns, so one MMA per code tile yields both parts.
         uint32_t b0[8][2], b1[8][2];
         float accz[4] = {0.f, 0.f, 0.f, 0.f}, accy[4] = {0.f, 0.f, 0.f, 0.f};
         const int gph = ngw > 1 ? ngw / 2 : 1;                 // groups per half tile: 4 / 2 / 1
@@ -412,7 +397,14 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
             const __half2 y01 = __hmul2(q01, z01), y89 = __hmul2(q89, z89);
             mma16816(accz, ones, ones, ones, ones, as_u32(y01), as_u32(y89));
             mma16816(accy, ones, ones, ones, ones, as_u32(__hfma2(q01, z01, __hneg2(y01))), as_u32(__hfma2(q89, z89, __hneg2(y89))));
-            {
+            if constexpr (KB == 3) {
+                const __half2 s01 = as_h2(r0), s89 = as_h2(r1);
+                const __half2 p01 = __hmul2(q01, s01), p89 = __hmul2(q89, s89);
+                b0[ksx][0] = as_u32(p01);
+                b0[ksx][1] = as_u32(p89);
+                b1[ksx][0] = as_u32(__hfma2(q01, s01, __hneg2(p01)));
+                b1[ksx][1] = as_u32(__hfma2(q89, s89, __hneg2(p89)));
+            } else {
                 const __half2 sa01 = as_h2(__shfl_sync(0xffffffffu, r0, src0)), sa89 = as_h2(__shfl_sync(0xffffffffu, r1, src0));
                 const __half2 sb01 = as_h2(__shfl_sync(0xffffffffu, r0, src1)), sb89 = as_h2(__shfl_sync(0xffffffffu, r1, src1));
                 const __half2 pa01 = __hmul2(q01, sa01), pa89 = __hmul2(q89, sa89);
@@ -452,19 +444,21 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
             for (int k = 0; k < G::KSPS; ++k) {
                 const int ksx = st * G::KSPS + k;
                 if constexpr (KB == 3) {
+                    uint32_t w[4];
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        uint32_t u[4];
+                    for (int r = 0; r < 4; ++r) w[r] = lds32(src + (k * 16 + (r & 1) + (r >> 1) * 8) * G::RS);
+                    uint32_t rlo[F::N], rhi[F::N];
+                    F::unpack(w[0], w[1], rlo);
+                    F::unpack(w[2], w[3], rhi);
 #pragma unroll
-                        for (int r = 0; r < 4; ++r)
-                            u[r] = lds32(src + (k * 16 + (r & 1) + (r >> 1) * 8) * G::RS + h * 16) >> sh3;
-                        uint32_t rlo[6], rhi[6];
-                        unpack3_alternate(u[0], u[1], rlo);
-                        unpack3_alternate(u[2], u[3], rhi);
+                    for (int i = 0; i < F::N; i += 2) {
+                        const uint32_t a1 = (i + 1 < F::N) ? rlo[i + 1] : 0u, a3 = (i + 1 < F::N) ? rhi[i + 1] : 0u;
+                        mma16816(acc[i / 2], rlo[i], a1, rhi[i], a3, b0[ksx][0], b0[ksx][1]);
+                    }
 #pragma unroll
-                        for (int j = 0; j < 3; ++j)
-                            mma16816(acc[h * 3 + j], rlo[2 * j], rlo[2 * j + 1], rhi[2 * j], rhi[2 * j + 1],
-                                     h ? b1[ksx][0] : b0[ksx][0], h ? b1[ksx][1] : b0[ksx][1]);
+                    for (int i = 0; i < F::N; i += 2) {
+                        const uint32_t a1 = (i + 1 < F::N) ? rlo[i + 1] : 0u, a3 = (i + 1 < F::N) ? rhi[i + 1] : 0u;
+                        mma16816(acc[i / 2], rlo[i], a1, rhi[i], a3, b1[ksx][0], b1[ksx][1]);
                     }
                 } else {
                     constexpr int NF = (KB == 1) ? 16 : F::N;              // fields used per word (1-bit: one 16-bit half)
@@ -500,32 +494,24 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
 
         // ---- epilogue ----------------------------------------------------------------------------------
         if constexpr (KB == 3) {
-            // octets g and g+4 of half h work on group 4h + cp of the tile (cp = g & 3): tokens tok0 + field, the lower
-            // octet's rows holding fields 4j, 4j+2, the upper one's 4j+1, 4j+3; hi and lo sums are the column pair cp
-            constexpr int P6[6] = {0, 6, 6, 2, 8, 8};          // bit position of the field in each unpacked register
-            const int cp = g & 3, fodd = g >> 2;
+            // the octet's column is n = g, held by the lane with tig == g/2
+            const int tok0 = tile0 + g * G::TPO;               // first token of this octet's chunk
+            if (tok0 < hi && tig == (g >> 1)) {                // chunks are whole or absent (hi is a group multiple)
+                const bool sel = g & 1;
+                const float corr = sel ? accz[1] : accz[0];
+                float *dst = sm.scores + (tok0 - t0);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int grp = 4 * h + cp;
-                const int zsrc = (lane & ~3) | ((grp >> 1) & 3);
-                const float z0 = __shfl_sync(0xffffffffu, accz[0], zsrc), z1 = __shfl_sync(0xffffffffu, accz[1], zsrc);
-                const float corr = (grp & 1) ? z1 : z0;
-                const int tok0 = tile0 + 44 * h + 11 * cp;
-                if (tok0 < hi && tig == cp) {                  // 11-token groups are whole or absent
-                    float *dst = sm.scores + (tok0 - t0);
-#pragma unroll
-                    for (int j = 0; j < 3; ++j) {
-                        const int f0 = 4 * j + fodd, f1 = f0 + 2;
-                        float s0 = fmaf(acc[h * 3 + j][0] + acc[h * 3 + j][1], (float)(1 << (24 - P6[2 * j])), corr);
-                        float s1 = fmaf(acc[h * 3 + j][2] + acc[h * 3 + j][3], (float)(1 << (24 - P6[2 * j + 1])), corr);
-                        if (a.round_scores) {
-                            const float2 r = __half22float2(__floats2half2_rn(s0, s1));
-                            s0 = r.x;
-                            s1 = r.y;
-                        }
-                        dst[f0] = s0 * a.softmax_scale;
-                        if (f1 <= 10) dst[f1] = s1 * a.softmax_scale;
+                for (int m = 0; m < G::NMMA; ++m) {
+                    const int i0 = 2 * m, i1 = 2 * m + 1;
+                    float s0 = fmaf(sel ? acc[m][1] : acc[m][0], (float)(1 << (24 - F::pos(i0 % F::N))), corr);
+                    float s1 = (i1 < G::TPO) ? fmaf(sel ? acc[m][3] : acc[m][2], (float)(1 << (24 - F::pos(i1 % F::N))), corr) : 0.f;
+                    if (a.round_scores) {
+                        const float2 r = __half22float2(__floats2half2_rn(s0, s1));
+                        s0 = r.x;
+                        s1 = r.y;
                     }
+                    dst[i0] = s0 * a.softmax_scale;
+                    if (i1 < G::TPO) dst[i1] = s1 * a.softmax_scale;
                 }
             }
         } else {
