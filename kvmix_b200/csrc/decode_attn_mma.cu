@@ -163,6 +163,45 @@ template <> struct VFields<1> {
     }
 };
 
+// Value-side extraction from ONE register that already pairs two 16-bit half-words along the contraction axis (as
+// a transposing ldmatrix delivers them): r[i] = fp16x2 of field i of both half-words, i < 16 / BITS, each left at
+// bit position pos(i) >= 4 (>= 2 for 4-bit codes) of its half -- the positions VFields uses, for the same reason.
+template <int BITS> struct VHalf;
+template <> struct VHalf<4> {
+    static constexpr int N = 4;
+    __device__ static __forceinline__ int pos(int i) { return (i & 1) ? 6 : 2; }
+    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[4]) {
+        const uint32_t xu = x << 2, xd = x >> 6;
+        r[0] = xu & 0x003c003cu; r[1] = xu & 0x03c003c0u; r[2] = xd & 0x003c003cu; r[3] = xd & 0x03c003c0u;
+    }
+};
+template <> struct VHalf<2> {
+    static constexpr int N = 8;
+    __device__ static __forceinline__ int pos(int i) { return i < 2 ? 6 + 2 * i : i < 5 ? 2 * i : 2 * i - 6; }
+    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[8]) {
+        const uint32_t xu = x << 6, xd = x >> 6;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) r[t] = xu & (0x00030003u << (6 + 2 * t));
+#pragma unroll
+        for (int t = 2; t < 5; ++t) r[t] = x & (0x00030003u << (2 * t));
+#pragma unroll
+        for (int t = 5; t < 8; ++t) r[t] = xd & (0x00030003u << (2 * t - 6));
+    }
+};
+template <> struct VHalf<1> {
+    static constexpr int N = 16;
+    __device__ static __forceinline__ int pos(int i) { return i < 4 ? i + 6 : i < 10 ? i : i - 6; }
+    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[16]) {
+        const uint32_t xu = x << 6, xd = x >> 6;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) r[t] = xu & (0x00010001u << (t + 6));
+#pragma unroll
+        for (int t = 4; t < 10; ++t) r[t] = x & (0x00010001u << t);
+#pragma unroll
+        for (int t = 10; t < 16; ++t) r[t] = xd & (0x00010001u << (t - 6));
+    }
+};
+
 // ---------------------------------------------------------------------------------------------
 // Key-side geometry per bit width.  A warp tile is 8 lane-octets x TPO tokens; code words reach the
 // warp through its own ring of cp.async stages in shared memory (padded rows so the fragment loads
@@ -566,13 +605,13 @@ template <int VB, int MODE>
 __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int32_t *vc, const __half *vs,
                                               const __half *vz, const MmaSmem &sm, int t0, int hi) {
     using G = VGeom<VB>;
-    using F = VFields<VB>;
-    constexpr int WPO = (VB == 4) ? 2 : 1;                    // words per octet (16 channels)
-    constexpr int NF = (VB == 1) ? 16 : F::N;                 // fields used per word (1-bit: one 16-bit half)
+    using F = VHalf<VB>;
+    constexpr int NB = G::GPT;                                // 16-byte blocks per token row: 1 / 2 / 4
+    constexpr int CPB = kHeadDim / NB;                        // channels per block: 128 / 64 / 32
+    constexpr int MPB = F::N / 2;                             // MMAs (channel pairs per octet) per block: 8 / 4 / 2
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
     const int Gv = a.v_group;
     const int ngv = kHeadDim / Gv;                            // channel groups: 4 / 2 / 1
-    const int grp = (16 * g) / Gv;                            // channel group of this octet
     const int n_blocks = (hi - t0 + G::TPS - 1) / G::TPS;
     const int my_blocks = (n_blocks - warp + kMmaWarps - 1) / kMmaWarps;
     float *my_red = reinterpret_cast<float *>(sm.ring);
@@ -587,19 +626,23 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     const uint32_t pb_s = ring_s + G::PB_OFF;
     // cp.async: granule x = lane + 32 i -> token row tl = x / GPT, granule gr = x % GPT (source is contiguous)
     const int cp_tl0 = lane / G::GPT, cp_gr = lane % G::GPT;
-    const int cp_grs = (VB == 4) ? (cp_gr ^ (2 * ((cp_tl0 >> 1) & 1))) : cp_gr;          // bank swizzle (4-bit rows)
+    // rows are XOR-swizzled by token so that the 8 rows x 16 bytes of every ldmatrix tile hit all 32 banks once
+    auto swz = [](int tl) { return (VB == 4) ? ((tl >> 1) & 3) : (VB == 2) ? ((tl >> 2) & 1) : 0; };
+    const int cp_grs = cp_gr ^ swz(cp_tl0);                                              // (tl + 8 k, 16 k keep the swizzle)
     const uint32_t cp_dst = ring_s + cp_tl0 * G::RBV + cp_grs * 16;                      // + slot*STAGE + i*(32/GPT)*RBV
-    // fragment loads: token tl = 16 h2 + tig + 4 i
-    uint32_t frag_s;
-    if (VB == 4) frag_s = ring_s + tig * G::RBV + (((g >> 1) ^ (2 * ((tig >> 1) & 1))) * 16) + (g & 1) * 8;   // swizzled granule
-    else if (VB == 2) frag_s = ring_s + tig * G::RBV + 4 * g;
-    else frag_s = ring_s + tig * G::RBV + 4 * (g >> 1);
-    const int wshift = (VB == 1) ? 16 * (g & 1) : 0;
-    // operand tile: pair pi = 8 h2 + 4 b + tig holds tokens (16 h2 + 8 b + tig, +4); reader column g
+    // fragment loads: one transposing ldmatrix hands lane (g, tig) the half-word g of a 16-byte block for the
+    // token pair (2 tig, 2 tig + 1) in one register, i.e. an A-fragment register pair along k without a byte permute.
+    // Tile j of an x4 load (lanes 8j .. 8j+7 give its row addresses): tokens 8 (j & 1) .. +7 of the k-step, block
+    // b0 + (j >> 1); the x2 load of 1-bit values has tiles j = 0, 1 only.
+    const int ldm_tl = 8 * ((lane >> 3) & 1) + (lane & 7);                               // + 16 h2
+    const int ldm_b = (lane >> 4) & (NB - 1);                                            // + b0 (4-bit: 0 or 2)
+    const uint32_t ldm_s0 = ring_s + ldm_tl * G::RBV + ((ldm_b ^ swz(ldm_tl)) * 16);
+    const uint32_t ldm_s1 = ring_s + ldm_tl * G::RBV + (((ldm_b + 2) & (NB - 1)) ^ swz(ldm_tl)) * 16;   // 4-bit: blocks 2, 3
+    // operand tile: pair pi = 8 h2 + 4 b + tig holds tokens (16 h2 + 8 b + 2 tig, +1); reader column g
     const uint32_t pb_rd = pb_s + (tig * 8 + g) * 4;                                     // + (8 h2 + 4 b) * 32
     // operand build: lane -> pair pi = lane & 15, column half ch = lane >> 4 (groups 2ch, 2ch+1)
     const int pi = lane & 15, ch = lane >> 4;
-    const int bt0 = 16 * (pi >> 3) + 8 * ((pi >> 2) & 1) + (pi & 3), bt1 = bt0 + 4;      // the pair's tokens in the stage
+    const int bt0 = 16 * (pi >> 3) + 8 * ((pi >> 2) & 1) + 2 * (pi & 3), bt1 = bt0 + 1;  // the pair's tokens in the stage
     // columns beyond the last channel group repeat that group: finite values in C columns nobody reads
     const int g0 = min(2 * ch, ngv - 1), g1 = min(2 * ch + 1, ngv - 1);
     const uint32_t o00 = ring_s + G::SZ_OFF + (bt0 * ngv + g0) * 2, o01 = ring_s + G::SZ_OFF + (bt0 * ngv + g1) * 2;
@@ -699,31 +742,32 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
             asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(pb_wr), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
         }
         __syncwarp();
-        const uint32_t fs = frag_s + st;
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
             const uint32_t b0 = lds32(pb_rd + (8 * h2) * 32), b1 = lds32(pb_rd + (8 * h2 + 4) * 32);
-            uint32_t w[4][WPO];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t ad = fs + (16 * h2 + 4 * i) * G::RBV;          // token 16 h2 + 4 i + tig (tig is in frag_s)
-                if constexpr (VB == 4) {
-                    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];\n" : "=r"(w[i][0]), "=r"(w[i][WPO - 1]) : "r"(ad));
-                } else {
-                    w[i][0] = lds32(ad) >> wshift;
-                }
+            // x[b][0] / x[b][1]: block b, tokens (2 tig, 2 tig + 1) / (2 tig + 8, 2 tig + 9) of the k-step
+            uint32_t x[NB][2];
+            const uint32_t ad = st + (16 * h2) * G::RBV;
+            if constexpr (VB == 1) {
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
+                             : "=r"(x[0][0]), "=r"(x[0][1]) : "r"(ldm_s0 + ad));
+            } else {
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(x[0][0]), "=r"(x[0][1]), "=r"(x[1][0]), "=r"(x[1][1]) : "r"(ldm_s0 + ad));
+                if constexpr (VB == 4)
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                                 : "=r"(x[NB - 2][0]), "=r"(x[NB - 2][1]), "=r"(x[NB - 1][0]), "=r"(x[NB - 1][1])
+                                 : "r"(ldm_s1 + ad));
             }
             mma16816(accz, ones, ones, ones, ones, b0, b1);
 #pragma unroll
-            for (int x = 0; x < WPO; ++x) {
+            for (int bb = 0; bb < NB; ++bb) {
                 uint32_t rlo[F::N], rhi[F::N];
-                F::unpack(w[0][x], w[1][x], rlo);              // tokens (tig, tig+4)    -> k cols 2tig, 2tig+1
-                F::unpack(w[2][x], w[3][x], rhi);              // tokens (tig+8, tig+12) -> k cols 2tig+8, 2tig+9
+                F::unpack(x[bb][0], rlo);
+                F::unpack(x[bb][1], rhi);
 #pragma unroll
-                for (int i = 0; i < NF; i += 2) {
-                    const int m = (x * NF + i) / 2;
-                    mma16816(acc[m], rlo[i], rlo[i + 1], rhi[i], rhi[i + 1], b0, b1);
-                }
+                for (int i = 0; i < F::N; i += 2)              // rows g / g+8: channels bb*CPB + g*F::N + i / + i + 1
+                    mma16816(acc[bb * MPB + i / 2], rlo[i], rlo[i + 1], rhi[i], rhi[i + 1], b0, b1);
             }
         }
         __syncwarp();
@@ -736,17 +780,18 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     cp_async_wait<0>();
     __syncwarp();
     STALL_STORE(7);
-    // epilogue: channel c = 16 g + i (i = 2m + r); columns 2*grp (sum p*scale) and 2*grp+1 (sum p*mid) sit in tig == grp
-    if (tig == grp) {
-        float *red = my_red + 16 * g;
-        const float corr = (sumz[1] - G::MID * sumz[0]) * (1.f / 256.f);          // undo the 2^8 carried by the B operands
+    // epilogue: accumulator m = bb * MPB + ip holds channels c = bb*CPB + g*F::N + 2 ip (+1) in rows g (g+8); the column
+    // of its group grp = c / Gv (sum p*scale) and the group's correction (sum p*mid, sum p*scale) sit in the lane with
+    // tig == grp
+    const float corr = (sumz[1] - G::MID * sumz[0]) * (1.f / 256.f);              // undo the 2^8 carried by the B operands
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
+    for (int bb = 0; bb < NB; ++bb) {
+        const int c0 = bb * CPB + g * F::N;
+        if (tig == c0 / Gv) {                                                       // F::N <= 16 <= Gv: one group per octet block
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const int i = 2 * m + r;
-                const int fi = i % NF;
-                red[i] = fmaf(sum[m][r], (float)(1 << (16 - F::pos(fi))), corr);
+            for (int ip = 0; ip < MPB; ++ip) {
+                my_red[c0 + 2 * ip] = fmaf(sum[bb * MPB + ip][0], (float)(1 << (16 - F::pos(2 * ip))), corr);
+                my_red[c0 + 2 * ip + 1] = fmaf(sum[bb * MPB + ip][1], (float)(1 << (16 - F::pos(2 * ip + 1))), corr);
             }
         }
     }
