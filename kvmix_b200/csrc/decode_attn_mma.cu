@@ -9,7 +9,8 @@
 // all other bits masked off, *is* an fp16 number with value field * 2^(pos-24) (subnormals and the first normal
 // binade are linear in the bit pattern).  mma.sync multiplies such inputs exactly and accumulates in fp32, so the
 // product with the fp16 operand is exact and the power of two is undone per output row in the epilogue.  Pairs
-// along the contraction axis are formed with one byte-permute of two words.
+// along the contraction axis arrive ready-made from transposing ldmatrix loads (values; 1- and 2-bit keys) or are
+// formed with one byte-permute of two words (3- and 4-bit keys).
 //
 // Keys (codes [D, T/fpi], one word = fpi tokens of one channel; scale/zero [D, T/G]):
 //   A (16x16) = codes, rows = tokens, cols = 16 channels.  q[d]*scale[d,g] is carried as an exact fp16 pair hi + lo.
@@ -161,6 +162,42 @@ template <> struct VFields<1> {
 #pragma unroll
         for (int t = 10; t < 16; ++t) { r[t] = lod & (0x00010001u << (t - 6)); r[16 + t] = hid & (0x00010001u << (t - 6)); }
     }
+};
+
+// Key-side extraction from ONE register that already pairs the same 16-bit half-word of two channel rows (as a
+// transposing ldmatrix delivers them): r[i] = fp16x2 of field i of both half-words, i < 16 / BITS, at bit position
+// Fields<BITS>::pos(i).
+template <int BITS> struct KHalf;
+template <> struct KHalf<4> {
+    static constexpr int N = 4;
+    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[4]) {
+        const uint32_t xs = x >> 8;
+        r[0] = x & 0x000f000fu; r[1] = x & 0x00f000f0u; r[2] = xs & 0x000f000fu; r[3] = xs & 0x00f000f0u;
+    }
+};
+template <> struct KHalf<2> {
+    static constexpr int N = 8;
+    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[8]) {
+        const uint32_t xs = x >> 10;
+#pragma unroll
+        for (int t = 0; t < 5; ++t) r[t] = x & (0x00030003u << (2 * t));
+#pragma unroll
+        for (int t = 5; t < 8; ++t) r[t] = xs & (0x00030003u << (2 * (t - 5)));
+    }
+};
+template <> struct KHalf<1> {
+    static constexpr int N = 16;
+    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[16]) {
+        const uint32_t xs = x >> 10;
+#pragma unroll
+        for (int t = 0; t < 10; ++t) r[t] = x & (0x00010001u << t);
+#pragma unroll
+        for (int t = 10; t < 16; ++t) r[t] = xs & (0x00010001u << (t - 10));
+    }
+};
+template <> struct KHalf<3> {                       // 3-bit keys do not use this path (11 fields do not split into half-words)
+    static constexpr int N = 2;
+    __device__ static __forceinline__ void unpack(uint32_t, uint32_t (&)[2]) {}
 };
 
 // Value-side extraction from ONE register that already pairs two 16-bit half-words along the contraction axis (as
@@ -344,13 +381,20 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     const uint32_t sz_s = ring_s + G::NS * G::STAGE_BYTES;                    // [2][128][8] halfs
     const int gr = lane % G::GPR, row0 = lane / G::GPR;
     const uint32_t cp_dst = ring_s + row0 * G::RS + gr * 16;                   // + slot*STAGE + i*RPI*RS
-    // 3-bit: octet g owns the word of group g (11 tokens).  Other widths: the tile is worked as two halves of 128
-    // tokens, octet g owning tokens [128 h + 16 g, +16) of half h, so that the 16 rows of one MMA touch at most four
-    // groups and the eight B columns can carry {hi, lo} of q*scale for those four side by side.
-    constexpr int HW = (KB == 4) ? 2 : 1;                                      // code words per octet per half
-    const uint32_t frag_s = (KB == 3) ? ring_s + (2 * tig) * G::RS + g * 4
-                                      : ring_s + (2 * tig) * G::RS + ((KB == 4) ? 8 * g : (KB == 2) ? 4 * g : 4 * (g >> 1));
-    const int wshift = (KB == 1) ? 16 * (g & 1) : 0;
+    // 3-bit: octet g owns the word of group g (11 tokens), fetched with plain 32-bit loads.
+    // Other widths: code fragments come from transposing ldmatrix loads.  A channel row of the tile is NBK blocks of
+    // 16 bytes; one x4 load covers channel rows 16 ksx + (0..7 | 8..15) x two neighbouring blocks and hands lane
+    // (g, tig) the half-word g of each block for the channel pair (2 tig, 2 tig + 1) [+8]: an A-fragment register pair
+    // along k without a byte permute.  Octet g of block bb therefore owns tokens bb * 8 FH + g * FH .. + FH - 1
+    // (FH = 16 / bits fields per half-word).  The first NBK / 2 blocks are the first 128 tokens: their MMA rows touch
+    // at most four groups, so the eight B columns carry {hi, lo} of q*scale for those four side by side (b0); the
+    // other blocks use b1.
+    constexpr int FH = (KB == 3) ? 2 : 16 / KB;                                // fields per half-word: 4 / 8 / 16
+    constexpr int NBK = G::RB / 16;                                            // 16-byte blocks per channel row: 8 / 4 / 2
+    constexpr int MPB = FH / 2;                                                // MMAs per block and k-step: 2 / 4 / 8
+    constexpr int HW = 2;                                                      // 4-bit: code words per octet per half
+    const uint32_t frag_s = ring_s + (2 * tig) * G::RS + ((KB == 4) ? 8 * g : 4 * g);   // 3-bit and 4-bit (plain loads)
+    const uint32_t ldk_s = ring_s + ((lane & 7) + 8 * ((lane >> 3) & 1)) * G::RS + (lane >> 4) * 16;   // + k*16*RS + 32*pair
     // ldmatrix.x4 row addresses: lanes 0-7 scale rows 16ksx+0..7, 8-15 scale rows +8..15, 16-31 the same of the zero tile
     const uint32_t ldm_s = sz_s + (((lane >> 3) & 1) * 8 + (lane & 7)) * 16 + (lane >> 4) * 2048;
     const uint32_t q_s = smem_u32(sm.q) + (2 * tig) * 2;                       // + 32 ksx [+16]
@@ -499,19 +543,17 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
                         const uint32_t a1 = (i + 1 < F::N) ? rlo[i + 1] : 0u, a3 = (i + 1 < F::N) ? rhi[i + 1] : 0u;
                         mma16816(acc[i / 2], rlo[i], a1, rhi[i], a3, b1[ksx][0], b1[ksx][1]);
                     }
-                } else {
-                    constexpr int NF = (KB == 1) ? 16 : F::N;              // fields used per word (1-bit: one 16-bit half)
+                } else if constexpr (KB == 4) {
+                    // 4-bit keys: two words (16 tokens) per octet and half, plain 64-bit loads + byte permutes (measured 1.5 %
+                    // faster than the ldmatrix form below for this width: 4 loads of 2 blocks each per k-step)
+                    constexpr int NF = F::N;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         uint32_t w[4][HW];
 #pragma unroll
                         for (int r = 0; r < 4; ++r) {
                             const uint32_t ad = src + (k * 16 + (r & 1) + (r >> 1) * 8) * G::RS + h * (G::RB / 2);
-                            if constexpr (HW == 2) {
-                                asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];\n" : "=r"(w[r][0]), "=r"(w[r][1]) : "r"(ad));
-                            } else {
-                                w[r][0] = lds32(ad) >> wshift;
-                            }
+                            asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];\n" : "=r"(w[r][0]), "=r"(w[r][1]) : "r"(ad));
                         }
 #pragma unroll
                         for (int x = 0; x < HW; ++x) {
@@ -524,6 +566,27 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
                                 if (h == 0) mma16816(acc[m], rlo[i], rlo[i + 1], rhi[i], rhi[i + 1], b0[ksx][0], b0[ksx][1]);
                                 else mma16816(acc[m], rlo[i], rlo[i + 1], rhi[i], rhi[i + 1], b1[ksx][0], b1[ksx][1]);
                             }
+                        }
+                    }
+                } else {
+                    using H = KHalf<KB>;
+                    const uint32_t lsrc = ldk_s + (st % G::NS) * G::STAGE_BYTES + (k * 16) * G::RS;
+#pragma unroll
+                    for (int pb2 = 0; pb2 < NBK / 2; ++pb2) {              // two blocks per load
+                        uint32_t x[2][2];
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                                     : "=r"(x[0][0]), "=r"(x[0][1]), "=r"(x[1][0]), "=r"(x[1][1]) : "r"(lsrc + pb2 * 32));
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const int bb = 2 * pb2 + u;
+                            uint32_t rlo[H::N], rhi[H::N];
+                            H::unpack(x[u][0], rlo);                        // channels 2tig, 2tig+1  -> k cols 2tig, 2tig+1
+                            H::unpack(x[u][1], rhi);                        // channels 2tig+8, +9    -> k cols 2tig+8, 2tig+9
+                            const uint32_t bx = (bb >= NBK / 2) ? b1[ksx][0] : b0[ksx][0];
+                            const uint32_t by = (bb >= NBK / 2) ? b1[ksx][1] : b0[ksx][1];
+#pragma unroll
+                            for (int i = 0; i < H::N; i += 2)
+                                mma16816(acc[bb * MPB + i / 2], rlo[i], rlo[i + 1], rhi[i], rhi[i + 1], bx, by);
                         }
                     }
                 }
@@ -553,10 +616,10 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
                     if (i1 < G::TPO) dst[i1] = s1 * a.softmax_scale;
                 }
             }
-        } else {
+        } else if constexpr (KB == 4) {
             // octet g of half h is in group h*gph + cp of the tile, cp = 16 g / Gk; its hi and lo sums are the column
             // pair cp, held by the lane with tig == cp; the group's zero term sits in another lane of the quad
-            constexpr int NF = (KB == 1) ? 16 : F::N;
+            constexpr int NF = F::N;
             const int cp = (16 * g) / Gk;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -578,6 +641,37 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
                             s1 = r.y;
                         }
                         *reinterpret_cast<float2 *>(dst + 2 * m) = make_float2(s0 * a.softmax_scale, s1 * a.softmax_scale);
+                    }
+                }
+            }
+        } else {
+            // octet g of block bb owns tokens bb*8FH + g*FH ..; in its half of the tile they are in group cp, whose hi and
+            // lo sums are the column pair cp, held by the lane with tig == cp; the group's zero term sits in another
+            // lane of the quad
+            const int lgk = 31 - __clz(Gk);                    // group sizes are powers of two here
+#pragma unroll
+            for (int bb = 0; bb < NBK; ++bb) {
+                constexpr int kHalfBlocks = NBK / 2;
+                const int h = bb / kHalfBlocks;
+                const int cp = (((bb % kHalfBlocks) * 8 * FH) + g * FH) >> lgk;
+                const int grp = h * gph + cp;
+                const int zsrc = (lane & ~3) | ((grp >> 1) & 3);
+                const float z0 = __shfl_sync(0xffffffffu, accz[0], zsrc), z1 = __shfl_sync(0xffffffffu, accz[1], zsrc);
+                const float corr = (grp & 1) ? z1 : z0;
+                const int tok0 = tile0 + bb * 8 * FH + g * FH;
+                if (tok0 < hi && tig == cp) {                  // FH-token chunks are whole or absent (hi is a group multiple)
+                    float *dst = sm.scores + (tok0 - t0);
+#pragma unroll
+                    for (int ip = 0; ip < MPB; ++ip) {
+                        const int m = bb * MPB + ip;
+                        float s0 = fmaf(acc[m][0] + acc[m][1], (float)(1 << (24 - F::pos(2 * ip))), corr);
+                        float s1 = fmaf(acc[m][2] + acc[m][3], (float)(1 << (24 - F::pos(2 * ip + 1))), corr);
+                        if (a.round_scores) {
+                            const float2 r = __half22float2(__floats2half2_rn(s0, s1));
+                            s0 = r.x;
+                            s1 = r.y;
+                        }
+                        *reinterpret_cast<float2 *>(dst + 2 * ip) = make_float2(s0 * a.softmax_scale, s1 * a.softmax_scale);
                     }
                 }
             }
