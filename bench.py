@@ -31,7 +31,7 @@ SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.acti
 
 # DRAM traffic per (sequence, head) unit of one fused-attention launch: dram__bytes_read + dram__bytes_write of an
 # ncu capture of each kernel variant at B=32, context 4096 (one CTA per unit, so traffic is proportional to units).
-NCU_TRAFFIC_PER_UNIT = {(4, 4): 739.3e3, (3, 2): 657.5e3, (2, 2): 469.8e3}
+NCU_TRAFFIC_PER_UNIT = {(4, 4): 738.8e3, (3, 2): 656.7e3, (2, 2): 469.9e3}
 
 
 def measured_peak_gbs():
