@@ -48,7 +48,8 @@ static SplitPlan plan_splits_generic(int T, int k_bits, int64_t heads) {
 // remainder of up to a quarter step.  The chunk is the candidate with the best estimated throughput under a
 // model fitted to measurements on B200 (2-bit keys and values, 256..8192 CTAs of 1024..8192 tokens):
 //   rate ~ q / ceil(q) * chunk / (chunk + 670),  q = CTAs / (148 SMs * 3 resident CTAs),
-// i.e. whole waves of CTAs and a fixed cost per CTA worth 670 tokens (7 us against 10.5 us per 1000 tokens); chunks
+// i.e. whole waves of CTAs and a fitted per-CTA term worth 670 tokens (it absorbs launch ramp, tail and co-residency
+// effects: an undisturbed CTA shows no such fixed cost on the phase clock); chunks
 // under 4096 tokens measured a further ~10 % below that and more than one split pays for the counter reset and the
 // merge.  Ties go to fewer splits.
 constexpr int kMmaSlots = 148 * 3;
