@@ -220,6 +220,21 @@ class KVmixLayerCache:
                 self.vmn[:, :, :self.tvq].contiguous() if vq else None,
                 self.kv_seq_len)
 
+    def view_tuple(self):
+        """The upstream 9-tuple as views into the preallocated buffers (no copies of the packed tensors; the small
+        fp16 tails are gathered out of their rings).  The views are overwritten by later appends."""
+        kq = self.tkq > 0
+        vq = self.tvq > 0
+        return (self.kcode[..., :self.tkq // self.fk] if kq else None,
+                self._ring(self.kfull, self.k_start, self.k_len, self.k_cap),
+                self.kscale[..., :self.tkq // self.k_group] if kq else None,
+                self.kmn[..., :self.tkq // self.k_group] if kq else None,
+                self.vcode[:, :, :self.tvq] if vq else None,
+                self._ring(self.vfull, self.v_start, self.v_len, self.v_cap),
+                self.vscale[:, :, :self.tvq] if vq else None,
+                self.vmn[:, :, :self.tvq] if vq else None,
+                self.kv_seq_len)
+
     def load_tuple(self, past_key_value):
         """Adopt an upstream 9-tuple (any of its tensors may be None): copies into the preallocated buffers."""
         kq, kfull, ksc, kmn, vq, vfull, vsc, vmn, seen = past_key_value
@@ -262,11 +277,49 @@ def kv_bytes_per_head(tkq, tvq, rk, rv, D, k_bits, k_group, v_bits, v_group):
     return kcodes + ksz + vcodes + vsz + resid
 
 
+class KVmixPast(tuple):
+    """Upstream's past_key_value 9-tuple backed by a preallocated KVmixLayerCache (``.cache``): element [8] is
+    kv_seq_len as upstream reads it, elements [0..7] are lazily built views for whoever indexes them.
+    ``attention_step(..., in_place=True)`` returns it and, given it back, appends in place and runs the fused
+    tensor-core attention instead of re-concatenating the packed tensors every step."""
+
+    def __new__(cls, cache):
+        self = super().__new__(cls, (None,) * 8 + (cache.kv_seq_len,))
+        self.cache = cache
+        self._views = None
+        return self
+
+    def __getitem__(self, i):
+        if isinstance(i, int) and (i == 8 or i == -1):
+            return tuple.__getitem__(self, 8)
+        if self._views is None:
+            self._views = self.cache.view_tuple()
+        return self._views[i]
+
+    def __iter__(self):
+        return iter(self[0:9])
+
+
+def _grown(cache, need_tokens):
+    """A cache with at least ``need_tokens`` capacity holding the same state (capacity doubles when it runs out)."""
+    if need_tokens <= cache.max_tokens:
+        return cache
+    pol = dict(residual_length=cache.window) if cache.window is not None else \
+        dict(k_residual_ratio=cache.rk, v_residual_ratio=cache.rv)
+    big = KVmixLayerCache(cache.B, cache.Hkv, cache.D, max(2 * cache.max_tokens, need_tokens + 1024), cache.k_bits,
+                          cache.v_bits, cache.v_group, device=cache.kfull.device, **pol)
+    big.load_tuple(cache.view_tuple())
+    return big
+
+
 def attention_step(query_states, key_states, value_states, past_key_value, k_bits, v_bits, group_size,
                    k_residual_ratio=None, v_residual_ratio=None, residual_length=None, use_cache=True,
-                   attention_mask=None):
+                   attention_mask=None, in_place=False):
     """Functional drop-in for upstream's attention body (modeling_llama_KVmix.py:105-273).
     attention_mask is upstream's additive mask ([B,1,q_len,kv_seq_len]); None means causal prefill / no padding.
+    in_place=True keeps the state in a preallocated KVmixLayerCache carried by the returned tuple (a KVmixPast): no
+    per-step concatenation, aligned buffers, the tensor-core kernel on every step.  The tuple's tensors are then
+    views that later steps overwrite; with in_place=False (default) every step returns fresh tensors as upstream does.
 
     query_states [B,nh,q_len,D], key_states/value_states [B,Hkv,q_len,D] (after RoPE);
     past_key_value is upstream's 9-tuple or None.  Returns (attn_output [B,nh,q_len,D], new 9-tuple).
@@ -278,6 +331,30 @@ def attention_step(query_states, key_states, value_states, past_key_value, k_bit
     Hkv = key_states.shape[1]
     k_group = 11 if k_bits == 3 else group_size
     v_group = group_size
+    if in_place or isinstance(past_key_value, KVmixPast):
+        # same contract, but the state lives in a preallocated cache carried by the returned tuple
+        pol = dict(residual_length=residual_length) if residual_length is not None else \
+            dict(k_residual_ratio=k_residual_ratio, v_residual_ratio=v_residual_ratio)
+        if past_key_value is None:
+            cache = KVmixLayerCache(B, Hkv, D, max(2 * q_len, q_len + 1024), k_bits, v_bits, group_size,
+                                    device=key_states.device, **pol)
+            cache.prefill(key_states, value_states)
+            attn = torch.nn.functional.scaled_dot_product_attention(
+                query_states, key_states, value_states, attn_mask=attention_mask,
+                is_causal=attention_mask is None and q_len > 1, enable_gqa=nh != Hkv, scale=1.0 / math.sqrt(D))
+        else:
+            if q_len != 1:
+                raise RuntimeError("cached attention takes one new token per step")
+            if isinstance(past_key_value, KVmixPast):
+                cache = past_key_value.cache
+            else:                                                  # a plain upstream tuple: adopt it once
+                seen = int(past_key_value[8])
+                cache = KVmixLayerCache(B, Hkv, D, max(2 * seen, seen + 1024), k_bits, v_bits, group_size,
+                                        device=key_states.device, **pol)
+                cache.load_tuple(past_key_value)
+            cache = _grown(cache, cache.kv_seq_len + 1)
+            attn = cache.decode_step(query_states, key_states, value_states, attention_mask=attention_mask)
+        return attn, (KVmixPast(cache) if use_cache else None)
     if past_key_value is not None:
         kq, kfull, ksc, kmn, vq, vfull, vsc, vmn, seen = past_key_value
         kv_seq_len = seen + q_len

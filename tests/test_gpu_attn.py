@@ -163,6 +163,47 @@ def test_nine_tuple_protocol_drop_in(cuda):
         assert_close_to_upstream(got.cpu().numpy(), want, ref.attend(q, ref_rounding=0))
 
 
+@pytest.mark.parametrize("policy", [dict(k_residual_ratio=0.2, v_residual_ratio=0.2), dict(residual_length=128)])
+def test_nine_tuple_protocol_in_place(cuda, policy):
+    """attention_step(in_place=True): the returned 9-tuple carries a preallocated cache; same results as the oracle,
+    kv_seq_len at [-1], packed tensors readable as views, and the cache grows when it runs out of capacity."""
+    import kvmix_b200 as kv
+    from kvmix_b200.cache import _grown
+    B, hkv, nh, L = 2, 2, 8, 300
+    k, v = make_kv(41, B, hkv, L + 50)
+    kt, vt = _t(k, cuda), _t(v, cuda)
+    ref = RefLayerCache(3, 2, 32, **policy)
+    ref.prefill(k[:, :, :L], v[:, :, :L])
+    qp = torch.randn((B, nh, L, 128), dtype=torch.float16, device=cuda,
+                     generator=torch.Generator(device=cuda).manual_seed(154))
+    _, past = kv.attention_step(qp, kt[:, :, :L], vt[:, :, :L], None, 3, 2, 32, in_place=True, **policy)
+    assert isinstance(past, kv.KVmixPast) and past[-1] == L and len(past) == 9
+    for i in range(50):
+        t = L + i
+        q = make_q(t, B, nh)
+        want = ref.decode_step(q, k[:, :, t:t + 1], v[:, :, t:t + 1])
+        got, past = kv.attention_step(_t(q, cuda), kt[:, :, t:t + 1], vt[:, :, t:t + 1], past, 3, 2, 32, **policy)
+        assert past[8] == t + 1
+        assert_close_to_upstream(got.cpu().numpy(), want, ref.attend(q, ref_rounding=0))
+        if i == 20:                                            # force a reallocation in the middle of the run
+            small = past.cache
+            small.max_tokens = small.kv_seq_len                # pretend it is full
+            past = kv.KVmixPast(_grown(small, small.kv_seq_len + 1))
+            assert past.cache is not small
+    kq, kfull, ksc, kmn, vq, vfull, vsc, vmn, seen = past
+    assert seen == L + 50 and np.array_equal(kq.cpu().numpy(), ref.kcode) and np.array_equal(vq.cpu().numpy(), ref.vcode)
+    assert np.array_equal(kfull.cpu().numpy().view(np.uint16), ref.kfull.view(np.uint16))
+    # a plain upstream tuple is adopted on the first in-place step
+    plain = tuple(x.clone() if torch.is_tensor(x) else x for x in past)
+    q = make_q(999, B, nh)
+    t = L + 50
+    k2, v2 = make_kv(42, B, hkv, 1)
+    want = ref.decode_step(q, k2, v2)
+    got, past2 = kv.attention_step(_t(q, cuda), _t(k2, cuda), _t(v2, cuda), plain, 3, 2, 32, in_place=True, **policy)
+    assert isinstance(past2, kv.KVmixPast) and past2[-1] == t + 1
+    assert_close_to_upstream(got.cpu().numpy(), want, ref.attend(q, ref_rounding=0))
+
+
 def test_attention_argument_errors(cuda):
     import kvmix_b200 as kv
     z = lambda *s, dt=torch.float16: torch.zeros(s, dtype=dt, device=cuda)
