@@ -217,9 +217,9 @@ int kvq_gemv(const kvq_gemv_args *a, kvq_stream_t stream);
  * packed prefix first and the fp16 tail after it, i.e. chronological order, so a left-padding mask indexes
  * it directly.
  *
- * workspace: kvq_decode_attn_workspace_bytes(B, nh, T) bytes of device memory (split partials and
- * one counter per query head).  The call zeroes the counters itself; concurrent calls must not
- * share a workspace.
+ * workspace: kvq_decode_attn_workspace_bytes(B, nh, T) bytes of device memory (partials of heads held by
+ * several CTAs and one counter per query head).  The call zeroes the counters itself unless flags says they are
+ * ready; concurrent calls must not share a workspace.
  */
 typedef struct {
     int32_t B, nh, nh_kv, D;
@@ -252,20 +252,42 @@ typedef struct {
     const void *mask;
     int64_t mask_sB, mask_sH;
     int32_t mask_is_f32;
+    int32_t flags;                 /* KVQ_ATTN_* bits; 0 for the behaviour described above */
 } kvq_attn_args;
 
+/* flags: the counters at the start of the workspace are known to be zero -- cleared once with
+ * kvq_decode_attn_workspace_init and since then touched only by this library, whose kernels leave every counter
+ * they use at zero.  The call then skips its own clearing (one memset node less per decode step). */
+#define KVQ_ATTN_WORKSPACE_READY 1
+
 uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32_t T);
+/* Clears the counters of a workspace for B * nh query heads (asynchronously, on `stream`). */
+int kvq_decode_attn_workspace_init(void *workspace, uint64_t bytes, int32_t B, int32_t nh, kvq_stream_t stream);
 int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream);
 
 /*
- * How kvq_decode_attn would cut the token axis for B*nh query heads, T tokens and k_bits-bit keys (no upstream
- * counterpart: upstream's GEMV never splits a row): *chunk tokens per split, *n_splits splits per head, the last
- * one running to T.  tensor_core != 0 asks for the plan of the tensor-core kernel (aligned caches, see
- * kvq_decode_attn), 0 for the generic kernel's.  Host-only; returns KVQ_OK or KVQ_ERR_NULL / KVQ_ERR_BITS /
- * KVQ_ERR_SHAPE.
+ * How kvq_decode_attn would spread the call described by `a` (shapes, bit widths and group sizes are read; no pointer
+ * is dereferenced) over CTAs.  No upstream counterpart: upstream's GEMV never splits a row.
+ * The token axis of a head is cut into units of `unit` tokens.  Tensor-core kernels (tensor_core != 0; aligned caches,
+ * see kvq_decode_attn): kernel 1 gives every query head its own CTAs, kernel 2 lets the heads_per_cta query heads that
+ * share a kv head share CTAs (chosen when nh / nh_kv is 2 or a multiple of 4 and the group sizes allow it).  The
+ * first n_whole heads take one CTA each -- a multiple of the GPU's resident-CTA slots, so they fill whole waves -- and
+ * each of the remaining n_cut heads is cut into `segments` pieces of segment_units units, launched after them, so
+ * that the last wave of the grid consists of short CTAs and fills every slot whatever the batch size.  A head held
+ * by several CTAs is merged by the one that finishes last, in token order (results do not depend on timing).
+ * Generic kernel (tensor_core == 0): every head is cut into `segments` chunks of `unit` tokens, one CTA each.
+ * max_segment_tokens: most tokens one CTA holds.  Host-only; returns KVQ_OK or KVQ_ERR_NULL / KVQ_ERR_BITS /
+ * KVQ_ERR_SHAPE / KVQ_ERR_HEADS.
  */
-int kvq_decode_attn_plan(int32_t B, int32_t nh, int32_t T, int32_t k_bits, int32_t tensor_core, int32_t *chunk,
-                         int32_t *n_splits);
+typedef struct {
+    int32_t kernel;              /* 0 generic, 1 tensor-core, 2 tensor-core with grouped query heads */
+    int32_t heads_per_cta;
+    int32_t unit, units_per_head;
+    int32_t n_ctas, n_whole, n_cut;
+    int32_t segments, segment_units, max_segment_tokens;
+} kvq_attn_plan;
+
+int kvq_decode_attn_plan(const kvq_attn_args *a, int32_t tensor_core, kvq_attn_plan *out);
 
 /*
  * kvq_decode_attn for callers that have no device memory to give.  (No counterpart in upstream KVmix:

@@ -62,7 +62,15 @@ class AttnArgs(C.Structure):
                 ("vfull", vp), ("vf_sB", i64), ("vf_sH", i64), ("vf_sT", i64),
                 ("vf_cap", i32), ("vf_start", i32),
                 ("workspace", vp), ("workspace_bytes", u64),
-                ("mask", vp), ("mask_sB", i64), ("mask_sH", i64), ("mask_is_f32", i32)]
+                ("mask", vp), ("mask_sB", i64), ("mask_sH", i64), ("mask_is_f32", i32), ("flags", i32)]
+
+
+class AttnPlan(C.Structure):
+    _fields_ = [("kernel", i32), ("heads_per_cta", i32), ("unit", i32), ("units_per_head", i32), ("n_ctas", i32),
+                ("n_whole", i32), ("n_cut", i32), ("segments", i32), ("segment_units", i32), ("max_segment_tokens", i32)]
+
+
+ATTN_WORKSPACE_READY = 1
 
 
 _lib = None
@@ -97,7 +105,9 @@ def lib():
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(AppendFormArgs), vp]
         L.kvq_decode_attn_plan.restype = C.c_int
-        L.kvq_decode_attn_plan.argtypes = [i32, i32, i32, i32, i32, C.POINTER(i32), C.POINTER(i32)]
+        L.kvq_decode_attn_plan.argtypes = [C.POINTER(AttnArgs), i32, C.POINTER(AttnPlan)]
+        L.kvq_decode_attn_workspace_init.restype = C.c_int
+        L.kvq_decode_attn_workspace_init.argtypes = [vp, u64, i32, i32, vp]
         L.kvq_decode_attn_workspace_bytes.restype = u64
         L.kvq_decode_attn_workspace_bytes.argtypes = [i32, i32, i32]
         _lib = L
@@ -106,7 +116,7 @@ def lib():
 
 EXPORTS = ["kvq_version", "kvq_error_string", "kvq_last_cuda_error", "kvq_features_per_int",
            "kvq_quant_lastdim", "kvq_append_kv", "kvq_gemv", "kvq_decode_attn", "kvq_decode_attn_workspace_bytes",
-           "kvq_decode_attn_static", "kvq_decode_attn_plan", "kvq_append_k", "kvq_append_v"]
+           "kvq_decode_attn_static", "kvq_decode_attn_plan", "kvq_decode_attn_workspace_init", "kvq_append_k", "kvq_append_v"]
 
 
 def check(rc):

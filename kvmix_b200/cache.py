@@ -184,14 +184,16 @@ class KVmixLayerCache:
         ws = self._ws.get((nh, stream))
         if ws is None:
             need = int(self._lib.kvq_decode_attn_workspace_bytes(B, nh, self.max_tokens))
-            ws = self._ws[(nh, stream)] = torch.empty(need, dtype=torch.uint8, device=q.device)
+            # zeroed once: the kernels leave the per-head counters at zero, so a step needs no clearing launch
+            # (the layout is fixed for this cache: same B and nh on every call)
+            ws = self._ws[(nh, stream)] = torch.zeros(need, dtype=torch.uint8, device=q.device)
         a = self._att
         a.nh, a.T, a.Tkq, a.Tvq = nh, self.tkq + self.k_len, self.tkq, self.tvq
         a.round_scores = int(bool(round_scores))
         a.q, a.q_sB, a.q_sH = q.data_ptr(), q.stride(0), q.stride(1)
         a.out, a.o_sB, a.o_sH = out.data_ptr(), out.stride(0), out.stride(1)
         a.kf_start, a.vf_start = self.k_start, self.v_start
-        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        a.workspace, a.workspace_bytes, a.flags = ws.data_ptr(), ws.numel(), _lib.ATTN_WORKSPACE_READY
         a.mask, a.mask_sB, a.mask_sH, a.mask_is_f32 = ops.mask_fields(attention_mask, B, nh, a.T)
         _lib.check(self._lib.kvq_decode_attn(C.byref(a), C.c_void_p(stream)))
         ops.LAUNCHES[0] += 1

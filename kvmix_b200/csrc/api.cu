@@ -14,7 +14,7 @@ int record_cuda_error(cudaError_t e) {
 }
 }  // namespace kvq
 
-extern "C" int kvq_version(void) { return 101; }   // 101: kvq_attn_args gained the additive mask
+extern "C" int kvq_version(void) { return 102; }   // 102: kvq_attn_args.flags, kvq_attn_plan, workspace_init
 
 extern "C" int kvq_features_per_int(int bits) { return (bits >= 1 && bits <= 4) ? kvq::fields_per_word(bits) : 0; }
 

@@ -13,6 +13,7 @@
 //   4. writes (acc, max, sum) for its split; the last CTA of a head to finish (one counter per
 //      head) merges the splits in index order, so results are run-to-run identical.
 #include "common.cuh"
+#include "attn_plan.cuh"
 
 namespace kvq {
 
@@ -41,74 +42,6 @@ static SplitPlan plan_splits_generic(int T, int k_bits, int64_t heads) {
     p.chunk = chunk;
     p.n_splits = (T + chunk - 1) / chunk;
     return p;
-}
-
-// Tensor-core kernel: a CTA step is 4 warps x one 256-token key tile (88 tokens for 3-bit keys), so chunks are
-// multiples of 1024 (352) tokens, at most 8192 (8096) scores are held, and the last split runs to T, absorbing a
-// remainder of up to a quarter step.  The chunk is the candidate with the best estimated throughput under a
-// model fitted to measurements on B200 (2-bit keys and values, 256..8192 CTAs of 1024..8192 tokens):
-//   rate ~ q / ceil(q) * chunk / (chunk + 670),  q = CTAs / (148 SMs * 3 resident CTAs),
-// i.e. whole waves of CTAs and a fitted per-CTA term worth 670 tokens (it absorbs launch ramp, tail and co-residency
-// effects: an undisturbed CTA shows no such fixed cost on the phase clock); chunks
-// under 4096 tokens measured a further ~10 % below that and more than one split pays for the counter reset and the
-// merge.  Ties go to fewer splits.
-constexpr int kMmaSlots = 148 * 3;
-constexpr double kMmaCtaCost = 670.0;
-
-struct PlanMemo {
-    int T, kb;
-    int64_t heads;
-    SplitPlan plan;
-};
-
-static SplitPlan plan_splits_mma(int T, int k_bits, int64_t heads) {
-    const int unit = (k_bits == 3) ? 352 : 1024;
-    const int max_chunk = (k_bits == 3) ? 8096 : 8192;
-    static thread_local PlanMemo memo[4] = {};
-    static thread_local int next = 0;
-    for (const PlanMemo &m : memo)
-        if (m.T == T && m.kb == k_bits && m.heads == heads) return m.plan;
-
-    // no finer than ~16 CTAs per slot in total: bounds the search and the workspace
-    const int64_t n_cap = (16 * kMmaSlots + heads - 1) / heads;
-    SplitPlan best = {0, 0};
-    double best_rate = 0.0;
-    for (int chunk = (max_chunk / unit) * unit; chunk >= unit; chunk -= unit) {
-        int n = (T + chunk - 1) / chunk;
-        int last = T - (n - 1) * chunk;
-        if (n > 1 && last <= unit / 4) {
-            --n;
-            last += chunk;
-        }
-        if (n > n_cap && best.n_splits > 0) break;
-        const double q = (double)(heads * n) / kMmaSlots;
-        const double waves = (double)((heads * n + kMmaSlots - 1) / kMmaSlots);
-        const double longest = chunk > last ? chunk : last;
-        double rate = q / waves * ((double)T / n) / (longest + kMmaCtaCost);
-        if (longest < 4096) rate *= 0.9;
-        if (n > 1) rate *= 0.92;
-        if (rate > best_rate * 1.0001) {
-            best = {chunk, n};
-            best_rate = rate;
-        }
-    }
-    memo[next] = {T, k_bits, heads, best};
-    next = (next + 1) & 3;
-    return best;
-}
-
-// Upper bound of plan_splits_mma's split count for every T' <= T (the workspace is sized once for a cache).
-static int64_t max_splits_mma(int T, int k_bits, int64_t heads) {
-    const int unit = (k_bits == 3) ? 352 : 1024;
-    const int max_chunk = (k_bits == 3) ? 8096 : 8192;
-    const int64_t n_cap = (16 * kMmaSlots + heads - 1) / heads;
-    const int64_t by_unit = (T + unit - 1) / unit, by_max = (T + (max_chunk / unit) * unit - 1) / ((max_chunk / unit) * unit);
-    const int64_t n = by_unit < n_cap ? by_unit : n_cap;
-    return n > by_max ? n : by_max;
-}
-
-static SplitPlan plan_splits(int T, int k_bits, int64_t heads, bool mma_path = false) {
-    return mma_path ? plan_splits_mma(T, k_bits, heads) : plan_splits_generic(T, k_bits, heads);
 }
 
 struct Smem {
@@ -333,12 +266,65 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(kvq_attn_args
         }
         out[tid] = __float2half_rn(acc / L);
     }
+    if (tid == 0) counters[s] = 0u;                          // ready for the next launch
 }
 
-// tensor-core path (decode_attn_mma.cu)
+// tensor-core paths (decode_attn_mma.cu: one query head per segment; decode_attn_gqa.cu: the query heads of a kv
+// head share a segment)
 bool mma_path_eligible(const kvq_attn_args &a);
-int launch_decode_attn_mma(const kvq_attn_args &a, int chunk, int n_splits, float *parts, unsigned int *counters,
+AttnPlan plan_attn_mma(int T, int k_bits, long long heads);
+int launch_decode_attn_mma(const kvq_attn_args &a, const AttnPlan &plan, float *parts, unsigned int *counters,
                            cudaStream_t st);
+int gqa_heads_per_cta(const kvq_attn_args &a);
+AttnPlan plan_attn_gqa(int T, int k_bits, long long head_groups);
+int launch_decode_attn_gqa(const kvq_attn_args &a, const AttnPlan &plan, int qhv, float *parts, unsigned int *counters,
+                           cudaStream_t st);
+
+// Upper bound, over every shorter context and every kernel, of the partial results (one per query head and segment)
+// a call may hold: the generic kernel's heads x splits; for the tensor-core kernels either what the score buffers
+// force (a segment holds at most 8192 tokens, 2048 / 1760 when four query heads share it) or the planner's own cap of
+// kMaxCtaRounds waves of CTAs over the cut heads (attn_plan.cuh), whichever is larger.
+static int64_t max_partials_bound(int T, int64_t heads) {
+    int64_t n = heads;
+    for (int kb = 3; kb <= 4; ++kb) {
+        const int64_t g = heads * plan_splits_generic(T, kb, heads).n_splits;
+        n = g > n ? g : n;
+    }
+    const int64_t forced = heads * ((T + 1759) / 1760);
+    const int64_t capped = (int64_t)kMaxCtaRounds * kSmCount * 3 * 4 + heads;
+    n = forced > n ? forced : n;
+    return capped > n ? capped : n;
+}
+
+struct AttnLaunch {
+    bool use_mma;
+    int qhv;             // query heads per CTA (grouped kernel), 0 otherwise
+    AttnPlan mplan;
+    SplitPlan gplan;
+    int64_t heads, ctas, partials;
+};
+
+static AttnLaunch plan_launch(const kvq_attn_args &a) {
+    AttnLaunch L = {};
+    L.heads = (int64_t)a.B * a.nh;
+    L.use_mma = mma_path_eligible(a);
+    L.qhv = L.use_mma ? gqa_heads_per_cta(a) : 0;
+    L.gplan = {0, 1};
+    if (L.qhv) {
+        L.mplan = plan_attn_gqa(a.T, a.k_bits, L.heads / L.qhv);
+        L.ctas = (int64_t)L.mplan.n_whole + (int64_t)L.mplan.n_cut * L.mplan.k;
+        L.partials = L.mplan.k > 1 ? (int64_t)L.mplan.n_cut * L.mplan.k * L.qhv : 0;
+    } else if (L.use_mma) {
+        L.mplan = plan_attn_mma(a.T, a.k_bits, L.heads);
+        L.ctas = (int64_t)L.mplan.n_whole + (int64_t)L.mplan.n_cut * L.mplan.k;
+        L.partials = L.mplan.k > 1 ? (int64_t)L.mplan.n_cut * L.mplan.k : 0;
+    } else {
+        L.gplan = plan_splits_generic(a.T, a.k_bits, L.heads);
+        L.ctas = L.heads * L.gplan.n_splits;
+        L.partials = L.gplan.n_splits > 1 ? L.ctas : 0;
+    }
+    return L;
+}
 
 }  // namespace kvq
 
@@ -346,27 +332,54 @@ extern "C" uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32
     using namespace kvq;
     if (B <= 0 || nh <= 0 || T <= 0) return 256;
     const int64_t heads = (int64_t)B * nh;
-    int64_t ns = 1;
-    for (int kb = 3; kb <= 4; ++kb) {
-        const int64_t g = plan_splits_generic(T, kb, heads).n_splits, m = max_splits_mma(T, kb, heads);
-        ns = g > ns ? g : ns;
-        ns = m > ns ? m : ns;
-    }
     uint64_t bytes = (uint64_t)heads * 4;
     bytes = (bytes + 255) / 256 * 256;
-    bytes += (uint64_t)heads * ns * kPartStride * 4;
+    bytes += (uint64_t)max_partials_bound(T, heads) * kPartStride * 4;
     return (bytes + 255) / 256 * 256;
 }
 
-extern "C" int kvq_decode_attn_plan(int32_t B, int32_t nh, int32_t T, int32_t k_bits, int32_t tensor_core,
-                                    int32_t *chunk, int32_t *n_splits) {
+extern "C" int kvq_decode_attn_workspace_init(void *workspace, uint64_t bytes, int32_t B, int32_t nh, kvq_stream_t stream) {
     using namespace kvq;
-    if (!chunk || !n_splits) return KVQ_ERR_NULL;
-    if (k_bits < 1 || k_bits > 4) return KVQ_ERR_BITS;
-    if (B <= 0 || nh <= 0 || T <= 0) return KVQ_ERR_SHAPE;
-    const SplitPlan p = plan_splits(T, k_bits, (int64_t)B * nh, tensor_core != 0);
-    *chunk = p.chunk;
-    *n_splits = p.n_splits;
+    if (!workspace) return KVQ_ERR_NULL;
+    if (B <= 0 || nh <= 0) return KVQ_OK;
+    const uint64_t cbytes = ((uint64_t)B * nh * 4 + 255) / 256 * 256;
+    if (bytes < cbytes) return KVQ_ERR_WORKSPACE;
+    return record_cuda_error(cudaMemsetAsync(workspace, 0, cbytes, reinterpret_cast<cudaStream_t>(stream)));
+}
+
+extern "C" int kvq_decode_attn_plan(const kvq_attn_args *a, int32_t tensor_core, kvq_attn_plan *out) {
+    using namespace kvq;
+    if (!a || !out) return KVQ_ERR_NULL;
+    if (a->k_bits < 1 || a->k_bits > 4 || a->v_bits < 1 || a->v_bits > 4) return KVQ_ERR_BITS;
+    if (a->B <= 0 || a->nh <= 0 || a->T <= 0) return KVQ_ERR_SHAPE;
+    if (a->nh_kv <= 0 || a->nh % a->nh_kv != 0) return KVQ_ERR_HEADS;
+    const int64_t heads = (int64_t)a->B * a->nh;
+    if (tensor_core) {
+        const int qhv = gqa_heads_per_cta(*a);
+        const AttnPlan p = qhv ? plan_attn_gqa(a->T, a->k_bits, heads / qhv) : plan_attn_mma(a->T, a->k_bits, heads);
+        out->kernel = qhv ? 2 : 1;
+        out->heads_per_cta = qhv ? qhv : 1;
+        out->unit = p.unit;
+        out->units_per_head = p.uph;
+        out->n_whole = p.n_whole;
+        out->n_cut = p.n_cut;
+        out->segments = p.k;
+        out->segment_units = p.seg_units;
+        out->n_ctas = p.n_whole + p.n_cut * p.k;
+        out->max_segment_tokens = p.n_scores;
+    } else {
+        const SplitPlan p = plan_splits_generic(a->T, a->k_bits, heads);
+        out->kernel = 0;
+        out->heads_per_cta = 1;
+        out->unit = p.chunk;
+        out->units_per_head = p.n_splits;
+        out->n_whole = 0;
+        out->n_cut = (int32_t)heads;
+        out->segments = p.n_splits;
+        out->segment_units = 1;
+        out->n_ctas = (int32_t)(heads * p.n_splits);
+        out->max_segment_tokens = p.chunk;
+    }
     return KVQ_OK;
 }
 
@@ -395,25 +408,26 @@ extern "C" int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream) {
     if (Rv > 0 && (reinterpret_cast<uintptr_t>(a->vfull) % 4 || a->vf_sB % 2 || a->vf_sH % 2 || a->vf_sT % 2))
         return KVQ_ERR_ALIGN;
 
-    const int64_t heads = (int64_t)a->B * a->nh;
-    const bool use_mma = mma_path_eligible(*a);
-    const SplitPlan plan = plan_splits(a->T, a->k_bits, heads, use_mma);
-    if (heads * plan.n_splits > 2147483647LL) return KVQ_ERR_UNSUPPORTED;
+    const AttnLaunch L = plan_launch(*a);
+    if (L.ctas > 2147483647LL) return KVQ_ERR_UNSUPPORTED;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     float *parts = nullptr;
     unsigned int *counters = nullptr;
-    if (plan.n_splits > 1) {
-        uint64_t cbytes = ((uint64_t)heads * 4 + 255) / 256 * 256;
-        uint64_t need = cbytes + (uint64_t)heads * plan.n_splits * kPartStride * 4;
+    if (L.partials > 0) {
+        uint64_t cbytes = ((uint64_t)L.heads * 4 + 255) / 256 * 256;
+        uint64_t need = cbytes + (uint64_t)L.partials * kPartStride * 4;
         if (!a->workspace || a->workspace_bytes < need) return KVQ_ERR_WORKSPACE;
         counters = static_cast<unsigned int *>(a->workspace);
         parts = reinterpret_cast<float *>(static_cast<char *>(a->workspace) + cbytes);
-        int rc = record_cuda_error(cudaMemsetAsync(counters, 0, (size_t)heads * 4, st));
-        if (rc) return rc;
+        // every kernel leaves the counters it used at zero; a workspace not yet vouched for is cleared here
+        if (!(a->flags & KVQ_ATTN_WORKSPACE_READY)) {
+            int rc = record_cuda_error(cudaMemsetAsync(counters, 0, (size_t)L.heads * 4, st));
+            if (rc) return rc;
+        }
     }
-    if (use_mma) return launch_decode_attn_mma(*a, plan.chunk, plan.n_splits, parts, counters, st);
-    decode_attn_kernel<<<(unsigned)(heads * plan.n_splits), kAttnThreads, 0, st>>>(*a, plan.chunk, plan.n_splits,
-                                                                                   parts, counters);
+    if (L.qhv) return launch_decode_attn_gqa(*a, L.mplan, L.qhv, parts, counters, st);
+    if (L.use_mma) return launch_decode_attn_mma(*a, L.mplan, parts, counters, st);
+    decode_attn_kernel<<<(unsigned)L.ctas, kAttnThreads, 0, st>>>(*a, L.gplan.chunk, L.gplan.n_splits, parts, counters);
     return check_launch();
 }
 
@@ -458,5 +472,6 @@ extern "C" int kvq_decode_attn_static(const kvq_attn_args *a, kvq_stream_t strea
     kvq_attn_args b = *a;
     b.workspace = scratch;
     b.workspace_bytes = KVQ_STATIC_SCRATCH_BYTES;
+    b.flags &= ~KVQ_ATTN_WORKSPACE_READY;                     // the shared array is cleared on every call
     return kvq_decode_attn(&b, stream);                    // zeroes the counters it uses on `stream`
 }

@@ -24,323 +24,11 @@
 // Code words and scale/zero rows stream through per-warp multi-stage cp.async rings in shared memory (128-bit
 // copies, several KB in flight per warp).  The fp16 key tail is scored on the tensor cores straight from global
 // memory; the softmax, the optional additive mask and the fp16 value tail run on the CUDA cores.
-#include "common.cuh"
+#include "attn_mma_common.cuh"
+#include "attn_plan.cuh"
 
 namespace kvq {
 
-constexpr int kMmaThreads = 128;
-constexpr int kMmaWarps = 4;
-
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t r;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-    return r;
-}
-
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-// ---------------------------------------------------------------------------------------------
-// Field extraction.  unpack(wa, wb, r): r[i] = fp16x2 { field i of wa (low), field i of wb (high) }
-// left at bit position pos(i) inside each 16-bit half, i.e. the subnormal pair
-// { f_a * 2^(pos-24), f_b * 2^(pos-24) }.  inv_scale(i) = 2^(24-pos(i)).
-template <int BITS> struct Fields;
-
-template <> struct Fields<4> {
-    static constexpr int N = 8;
-    __device__ static __forceinline__ int pos(int i) { return (i & 1) ? 4 : 0; }
-    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[8]) {
-        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
-        const uint32_t los = lo >> 8, his = hi >> 8;
-        r[0] = lo & 0x000f000fu; r[1] = lo & 0x00f000f0u; r[2] = los & 0x000f000fu; r[3] = los & 0x00f000f0u;
-        r[4] = hi & 0x000f000fu; r[5] = hi & 0x00f000f0u; r[6] = his & 0x000f000fu; r[7] = his & 0x00f000f0u;
-    }
-};
-
-template <> struct Fields<2> {
-    static constexpr int N = 16;
-    __device__ static __forceinline__ int pos(int i) { const int t = i & 7; return t < 5 ? 2 * t : 2 * (t - 5); }
-    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[16]) {
-        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
-        const uint32_t los = lo >> 10, his = hi >> 10;
-#pragma unroll
-        for (int t = 0; t < 5; ++t) { r[t] = lo & (0x00030003u << (2 * t)); r[8 + t] = hi & (0x00030003u << (2 * t)); }
-#pragma unroll
-        for (int t = 5; t < 8; ++t) {
-            r[t] = los & (0x00030003u << (2 * (t - 5)));
-            r[8 + t] = his & (0x00030003u << (2 * (t - 5)));
-        }
-    }
-};
-
-template <> struct Fields<1> {
-    static constexpr int N = 32;
-    __device__ static __forceinline__ int pos(int i) { const int t = i & 15; return t < 10 ? t : t - 10; }
-    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[32]) {
-        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
-        const uint32_t los = lo >> 10, his = hi >> 10;
-#pragma unroll
-        for (int t = 0; t < 10; ++t) { r[t] = lo & (0x00010001u << t); r[16 + t] = hi & (0x00010001u << t); }
-#pragma unroll
-        for (int t = 10; t < 16; ++t) { r[t] = los & (0x00010001u << (t - 10)); r[16 + t] = his & (0x00010001u << (t - 10)); }
-    }
-};
-
-// 3-bit words: fields 0..9 at bits 3i, field 10 (2 bits) at bit 30.
-template <> struct Fields<3> {
-    static constexpr int N = 11;
-    __device__ static __forceinline__ int pos(int i) {
-        constexpr int P[11] = {0, 3, 6, 0, 3, 0, 3, 6, 0, 3, 0};
-        return P[i];
-    }
-    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[11]) {
-        const uint32_t x0 = prmt(wa, wb, 0x5410), x1 = x0 >> 9;
-        const uint32_t y = prmt(wa >> 15, wb >> 15, 0x5410), y1 = y >> 9;
-        const uint32_t z1 = prmt(wa, wb, 0x7632) >> 14;
-        r[0] = x0 & 0x00070007u; r[1] = x0 & 0x00380038u; r[2] = x0 & 0x01c001c0u;
-        r[3] = x1 & 0x00070007u; r[4] = x1 & 0x00380038u;
-        r[5] = y & 0x00070007u; r[6] = y & 0x00380038u; r[7] = y & 0x01c001c0u;
-        r[8] = y1 & 0x00070007u; r[9] = y1 & 0x00380038u;
-        r[10] = z1 & 0x00030003u;
-    }
-};
-
-// Value-side field extraction: same contract as Fields, but every field is moved to bit position >= 4 (>= 2
-// for 4-bit codes) of its 16-bit half.  The tensor core aligns the 16 products of an MMA (and the accumulator) to
-// the largest operand EXPONENT and truncates what falls about 26 bits below it; a subnormal's exponent is fixed at
-// -14 however small its value, so a code parked in the lowest mantissa bits loses low product bits whenever a
-// neighbouring token's probability is larger.  The loss is always downwards, so over a long, diffuse softmax it
-// adds up to a bias (2e-5 of the non-negative code sum for 2-bit codes at position 0, a quarter of that per two
-// positions higher) which the centring of the codes amplifies.  Two more shifts per word pair keep it below the
-// fp32 accumulation error.
-template <int BITS> struct VFields;
-
-template <> struct VFields<4> {
-    static constexpr int N = 8;
-    __device__ static __forceinline__ int pos(int i) { return (i & 1) ? 6 : 2; }
-    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[8]) {
-        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
-        const uint32_t lou = lo << 2, lod = lo >> 6, hiu = hi << 2, hid = hi >> 6;
-        r[0] = lou & 0x003c003cu; r[1] = lou & 0x03c003c0u; r[2] = lod & 0x003c003cu; r[3] = lod & 0x03c003c0u;
-        r[4] = hiu & 0x003c003cu; r[5] = hiu & 0x03c003c0u; r[6] = hid & 0x003c003cu; r[7] = hid & 0x03c003c0u;
-    }
-};
-
-template <> struct VFields<2> {
-    static constexpr int N = 16;
-    __device__ static __forceinline__ int pos(int i) { const int t = i & 7; return t < 2 ? 6 + 2 * t : t < 5 ? 2 * t : 2 * t - 6; }
-    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[16]) {
-        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
-        const uint32_t lou = lo << 6, lod = lo >> 6, hiu = hi << 6, hid = hi >> 6;
-#pragma unroll
-        for (int t = 0; t < 2; ++t) { r[t] = lou & (0x00030003u << (6 + 2 * t)); r[8 + t] = hiu & (0x00030003u << (6 + 2 * t)); }
-#pragma unroll
-        for (int t = 2; t < 5; ++t) { r[t] = lo & (0x00030003u << (2 * t)); r[8 + t] = hi & (0x00030003u << (2 * t)); }
-#pragma unroll
-        for (int t = 5; t < 8; ++t) { r[t] = lod & (0x00030003u << (2 * t - 6)); r[8 + t] = hid & (0x00030003u << (2 * t - 6)); }
-    }
-};
-
-template <> struct VFields<1> {
-    static constexpr int N = 32;
-    __device__ static __forceinline__ int pos(int i) { const int t = i & 15; return t < 4 ? t + 6 : t < 10 ? t : t - 6; }
-    __device__ static __forceinline__ void unpack(uint32_t wa, uint32_t wb, uint32_t (&r)[32]) {
-        const uint32_t lo = prmt(wa, wb, 0x5410), hi = prmt(wa, wb, 0x7632);
-        const uint32_t lou = lo << 6, lod = lo >> 6, hiu = hi << 6, hid = hi >> 6;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) { r[t] = lou & (0x00010001u << (t + 6)); r[16 + t] = hiu & (0x00010001u << (t + 6)); }
-#pragma unroll
-        for (int t = 4; t < 10; ++t) { r[t] = lo & (0x00010001u << t); r[16 + t] = hi & (0x00010001u << t); }
-#pragma unroll
-        for (int t = 10; t < 16; ++t) { r[t] = lod & (0x00010001u << (t - 6)); r[16 + t] = hid & (0x00010001u << (t - 6)); }
-    }
-};
-
-// Key-side extraction from ONE register that already pairs the same 16-bit half-word of two channel rows (as a
-// transposing ldmatrix delivers them): r[i] = fp16x2 of field i of both half-words, i < 16 / BITS, at bit position
-// Fields<BITS>::pos(i).
-template <int BITS> struct KHalf;
-template <> struct KHalf<4> {
-    static constexpr int N = 4;
-    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[4]) {
-        const uint32_t xs = x >> 8;
-        r[0] = x & 0x000f000fu; r[1] = x & 0x00f000f0u; r[2] = xs & 0x000f000fu; r[3] = xs & 0x00f000f0u;
-    }
-};
-template <> struct KHalf<2> {
-    static constexpr int N = 8;
-    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[8]) {
-        const uint32_t xs = x >> 10;
-#pragma unroll
-        for (int t = 0; t < 5; ++t) r[t] = x & (0x00030003u << (2 * t));
-#pragma unroll
-        for (int t = 5; t < 8; ++t) r[t] = xs & (0x00030003u << (2 * (t - 5)));
-    }
-};
-template <> struct KHalf<1> {
-    static constexpr int N = 16;
-    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[16]) {
-        const uint32_t xs = x >> 10;
-#pragma unroll
-        for (int t = 0; t < 10; ++t) r[t] = x & (0x00010001u << t);
-#pragma unroll
-        for (int t = 10; t < 16; ++t) r[t] = xs & (0x00010001u << (t - 10));
-    }
-};
-template <> struct KHalf<3> {                       // 3-bit keys do not use this path (11 fields do not split into half-words)
-    static constexpr int N = 2;
-    __device__ static __forceinline__ void unpack(uint32_t, uint32_t (&)[2]) {}
-};
-
-// Value-side extraction from ONE register that already pairs two 16-bit half-words along the contraction axis (as
-// a transposing ldmatrix delivers them): r[i] = fp16x2 of field i of both half-words, i < 16 / BITS, each left at
-// bit position pos(i) >= 4 (>= 2 for 4-bit codes) of its half -- the positions VFields uses, for the same reason.
-template <int BITS> struct VHalf;
-template <> struct VHalf<4> {
-    static constexpr int N = 4;
-    __device__ static __forceinline__ int pos(int i) { return (i & 1) ? 6 : 2; }
-    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[4]) {
-        const uint32_t xu = x << 2, xd = x >> 6;
-        r[0] = xu & 0x003c003cu; r[1] = xu & 0x03c003c0u; r[2] = xd & 0x003c003cu; r[3] = xd & 0x03c003c0u;
-    }
-};
-template <> struct VHalf<2> {
-    static constexpr int N = 8;
-    __device__ static __forceinline__ int pos(int i) { return i < 2 ? 6 + 2 * i : i < 5 ? 2 * i : 2 * i - 6; }
-    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[8]) {
-        const uint32_t xu = x << 6, xd = x >> 6;
-#pragma unroll
-        for (int t = 0; t < 2; ++t) r[t] = xu & (0x00030003u << (6 + 2 * t));
-#pragma unroll
-        for (int t = 2; t < 5; ++t) r[t] = x & (0x00030003u << (2 * t));
-#pragma unroll
-        for (int t = 5; t < 8; ++t) r[t] = xd & (0x00030003u << (2 * t - 6));
-    }
-};
-template <> struct VHalf<1> {
-    static constexpr int N = 16;
-    __device__ static __forceinline__ int pos(int i) { return i < 4 ? i + 6 : i < 10 ? i : i - 6; }
-    __device__ static __forceinline__ void unpack(uint32_t x, uint32_t (&r)[16]) {
-        const uint32_t xu = x << 6, xd = x >> 6;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) r[t] = xu & (0x00010001u << (t + 6));
-#pragma unroll
-        for (int t = 4; t < 10; ++t) r[t] = x & (0x00010001u << t);
-#pragma unroll
-        for (int t = 10; t < 16; ++t) r[t] = xd & (0x00010001u << (t - 6));
-    }
-};
-
-// ---------------------------------------------------------------------------------------------
-// Key-side geometry per bit width.  A warp tile is 8 lane-octets x TPO tokens; code words reach the
-// warp through its own ring of cp.async stages in shared memory (padded rows so the fragment loads
-// are bank-conflict free), three stages in flight ahead of the math.  All shared-memory offsets are
-// compile-time constants relative to one per-lane base; global addresses advance by per-stage strides.
-template <int KB> struct KGeom {
-    static constexpr int FPI = fields_per_word(KB);
-    static constexpr int WPL = (KB == 4) ? 4 : (KB == 2) ? 2 : 1;     // words per octet: 32 tokens (11 for 3-bit)
-    static constexpr int TPO = WPL * FPI;                              // tokens per octet chunk
-    static constexpr int WT = 8 * TPO;                                 // tokens per warp tile (256 / 88)
-    static constexpr int KSPS = (KB == 4) ? 1 : 2;                     // k-steps (16 channels) per stage
-    static constexpr int NSTAGE = 8 / KSPS;                            // stages per warp tile: 8 / 4
-    static constexpr int NMMA = (TPO + 1) / 2;                         // MMAs (token pairs) per octet chunk
-    static constexpr int RB = 32 * WPL;                                // code bytes per channel row per warp tile
-    static constexpr int RS = RB + 16;                                 // padded row stride in the ring
-    static constexpr int ROWS = 16 * KSPS;                             // channel rows per stage
-    static constexpr int STAGE_BYTES = ROWS * RS;                      // 2304 / 2560 / 1536
-    static constexpr int GPR = RB / 16;                                // 16-byte granules per row: 8 / 4 / 2
-    static constexpr int GPL = ROWS * GPR / 32;                        // granules per lane per stage: 4 / 4 / 2
-    static constexpr int RPI = 32 / GPR;                               // rows between a lane's granules
-    static constexpr int NS = 4;                                       // ring slots (NSTAGE % NS == 0: slots are static)
-    static constexpr int P = NS - 1;                                   // stages in flight
-    static constexpr int SZ_BYTES = 2 * kHeadDim * 16;                 // scale + zero tile: 16 B per channel row
-    static constexpr int WARP_BYTES = NS * STAGE_BYTES + SZ_BYTES;
-    static constexpr float MID = (float)((1 << KB) - 1) * 0.5f;        // codes are centred on the group midpoint
-};
-
-template <int WPL> struct WordVec;
-template <> struct WordVec<1> { using T = uint32_t; };
-template <> struct WordVec<2> { using T = uint2; };
-template <> struct WordVec<4> { using T = uint4; };
-
-template <int VB> struct VGeom {
-    static constexpr int FPI = fields_per_word(VB);
-    static constexpr int RBV = kHeadDim / FPI * 4;                     // code bytes per token row: 64 / 32 / 16
-    static constexpr int TPS = 32;                                     // tokens per stage (2 k-steps)
-    static constexpr int GPT = RBV / 16;                               // granules per token row: 4 / 2 / 1
-    static constexpr int GPL = (TPS * GPT + 31) / 32;                  // code granules per lane per stage: 4 / 2 / 1
-    static constexpr int SZ_OFF = TPS * RBV;                           // scale rows, then zero rows (<= 4 groups each)
-    static constexpr int STAGE_BYTES = TPS * RBV + 2 * TPS * 4 * 2;
-    static constexpr int NS = (VB == 4) ? 4 : (VB == 2) ? 6 : 8;
-    static constexpr int P = NS - 1;
-    static constexpr int PB_OFF = NS * STAGE_BYTES;                    // operand tile p*scale / p*mid: 16 token pairs x 8 cols
-    static constexpr int WARP_BYTES = NS * STAGE_BYTES + 16 * 8 * 4;
-    static constexpr float MID = (float)((1 << VB) - 1) * 0.5f;
-};
-
-template <int KB, int VB> constexpr int warp_region_bytes() {
-    return KGeom<KB>::WARP_BYTES > VGeom<VB>::WARP_BYTES ? KGeom<KB>::WARP_BYTES : VGeom<VB>::WARP_BYTES;
-}
-
-template <int BYTES>
-__device__ __forceinline__ void cp_async(uint32_t smem_addr, const void *gmem) {
-    if constexpr (BYTES == 16) {
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem));
-    } else {
-        asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(smem_addr), "l"(gmem), "n"(BYTES));
-    }
-}
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
-    return v;
-}
-// {lo, hi} -> fp16x2, round to nearest, saturating to the largest finite fp16 instead of overflowing to inf
-__device__ __forceinline__ uint32_t pack_h2_sat(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-__device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
-__device__ __forceinline__ __half2 as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
-
-// Optional phase clock (build with -DKVQ_PHASE_TIMING): thread 0 of the first 4096 CTAs stamps %globaltimer at
-// the phase boundaries; kvq_debug_phases() copies the stamps out.  0 start, 1 q stored, 2 scores done, 3 softmax
-// done, 4 fp16 value tail done, 5 packed values done.
-#ifdef KVQ_PHASE_TIMING
-__device__ unsigned long long g_phase[4096 * 8];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define PHASE(i) do { if (threadIdx.x == 0 && blockIdx.x < 4096) g_phase[blockIdx.x * 8 + (i)] = gtime(); } while (0)
-// slots 6 / 7: nanoseconds warp 0 spent waiting for its key / value ring (cp.async.wait_group + warp barrier)
-#define STALL_DECL unsigned long long stall_ns = 0
-#define STALL_BEGIN const unsigned long long stall_t0 = gtime()
-#define STALL_END stall_ns += gtime() - stall_t0
-#define STALL_STORE(i) do { if (threadIdx.x == 0 && blockIdx.x < 4096) g_phase[blockIdx.x * 8 + (i)] = stall_ns; } while (0)
-#else
-#define PHASE(i)
-#define STALL_DECL
-#define STALL_BEGIN
-#define STALL_END
-#define STALL_STORE(i)
-#endif
 struct MmaSmem {
     float *scores;          // [n_scores]
     unsigned char *ring;    // this warp's region
@@ -440,7 +128,6 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     if (tail_lo < t1) qk_tail_mma(a, kf, sm, t0, tail_lo, t1);
 
     const uint32_t ones = 0x3c003c00u;
-    STALL_DECL;
     for (int j = 0; j < my_tiles; ++j) {
         const int tile0 = t0 + (j * kMmaWarps + warp) * G::WT;
         const bool have_next = j + 1 < my_tiles;
@@ -448,12 +135,8 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
         const bool ok_nxt = have_next && (wcol_cur + tile_words < n_words);
 
         // the scale/zero tile of this warp tile was committed at least 3 groups ago
-        {
-            STALL_BEGIN;
-            cp_async_wait<2>();
-            __syncwarp();
-            STALL_END;
-        }
+        cp_async_wait<2>();
+        __syncwarp();
         // ---- B fragments q*scale and the zero term sum_d q[d]*zero[d,g] ----------------------------------
         // q*scale needs 22 bits; it is carried as an fp16 pair hi + lo (lo = fma(q, s, -hi) is exact), so the key
         // side adds no rounding beyond the fp32 accumulation.  The zero term gets the same treatment and is summed
@@ -516,12 +199,8 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
             }
             if (st == 0 && have_next) issue_sz(ks_cur + tile_groups, kz_cur + tile_groups);
             cp_async_commit();
-            {
-                STALL_BEGIN;
-                cp_async_wait<G::P>();
-                __syncwarp();
-                STALL_END;
-            }
+            cp_async_wait<G::P>();
+            __syncwarp();
             const uint32_t src = frag_s + (st % G::NS) * G::STAGE_BYTES;
 #pragma unroll
             for (int k = 0; k < G::KSPS; ++k) {
@@ -683,7 +362,6 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
         kz_cur += tile_groups;
     }
     cp_async_wait<0>();
-    STALL_STORE(6);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -768,7 +446,6 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     };
 
     float acc[8][4], accz[4] = {0.f, 0.f, 0.f, 0.f};
-    STALL_DECL;
 #pragma unroll
     for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
     const uint32_t ones = 0x3c003c00u;
@@ -808,12 +485,8 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     for (int q = 0; q < my_blocks; ++q) {
         issue_stage(issue_st);
         cp_async_commit();
-        {
-            STALL_BEGIN;
-            cp_async_wait<G::P>();
-            __syncwarp();
-            STALL_END;
-        }
+        cp_async_wait<G::P>();
+        __syncwarp();
         // ---- B operands for the stage: 16 token pairs x 8 columns -----------------------------------
         {
             // p is scaled by 2^8 before the fp16 rounding so that the many small probabilities of a long, diffuse
@@ -873,7 +546,6 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
     flush();
     cp_async_wait<0>();
     __syncwarp();
-    STALL_STORE(7);
     // epilogue: accumulator m = bb * MPB + ip holds channels c = bb*CPB + g*F::N + 2 ip (+1) in rows g (g+8); the column
     // of its group grp = c / Gv (sum p*scale) and the group's correction (sum p*mid, sum p*scale) sit in the lane with
     // tig == grp
@@ -934,10 +606,11 @@ __device__ __forceinline__ void qk_tail_mma(const kvq_attn_args &a, const __half
 }
 
 // ---------------------------------------------------------------------------------------------
+// One segment: tokens [t0, t1) of query head (b, h); segment `seg` of the `cnt` the head is cut into.
 template <int KB, int VB>
-__global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_attn_args a, int chunk, int n_splits,
-                                                                     int n_scores, float *__restrict__ parts,
-                                                                     unsigned int *__restrict__ counters) {
+__device__ __forceinline__ void attn_segment(const kvq_attn_args &a, int n_scores, int s, int t0, int t1, int seg,
+                                             int cnt, int n_whole, float *__restrict__ parts,
+                                             unsigned int *__restrict__ counters) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     MmaSmem sm;
@@ -947,23 +620,14 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
     sm.tailred = reinterpret_cast<float *>(after_scores + kMmaWarps * warp_region_bytes<KB, VB>());
     sm.q = reinterpret_cast<__half *>(sm.tailred + kMmaWarps * kHeadDim);
     sm.misc = reinterpret_cast<float *>(sm.q + kHeadDim);
-
-    // split-major order: all heads' first splits, then their second ... ; the last split of a head is the short
-    // one (or absorbs a short remainder), so the grid's final wave is made of the cheapest CTAs
-    const int n_heads = a.B * a.nh;
-    const int split = blockIdx.x / n_heads;
-    const int s = blockIdx.x % n_heads;                       // b * nh + h
     const int b = s / a.nh, h = s % a.nh;
-    // grouped queries: each query head is its own CTA and reads kv head hk; the heads of one kv head are
-    // neighbouring CTAs, so the cache is fetched from HBM once and re-read from L2
+    // grouped queries: each query head is its own segment and reads kv head hk; the heads of one kv head are
+    // neighbouring units of work, so the cache is fetched from HBM once and re-read from L2
     const int hk = h / (a.nh / a.nh_kv);
-    const int t0 = split * chunk, t1 = (split == n_splits - 1) ? a.T : t0 + chunk;
 
-    PHASE(0);
     const __half *q = static_cast<const __half *>(a.q) + (int64_t)b * a.q_sB + (int64_t)h * a.q_sH;
     if (tid < kHeadDim) sm.q[tid] = q[tid];
     for (int i = tid; i < kMmaWarps * kHeadDim; i += kMmaThreads) sm.tailred[i] = 0.f;
-    PHASE(1);
 
     // ---- 1. scores ------------------------------------------------------------------------------
     {
@@ -986,7 +650,6 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
     const int v_hi = min(t1, a.Tvq);
     if (t0 < v_hi) pv_packed_mma<VB, 1>(a, vc, vs, vz, sm, t0, v_hi);   // start filling this warp's value ring now
     __syncthreads();
-    PHASE(2);
 
     // ---- 2. softmax numerators ------------------------------------------------------------------
     // The fp16 value tail of this split (the window: usually <= 128 tokens) is fetched into registers first, so its
@@ -1050,7 +713,6 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
     __syncthreads();
     l = (sm.misc[4] + sm.misc[5]) + (sm.misc[6] + sm.misc[7]);
 
-    PHASE(3);
     // ---- 3. p.V -----------------------------------------------------------------------------------
     if (v_lo < t1) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -1077,12 +739,10 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
             dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
         }
     }
-    PHASE(4);
     if (t0 < v_hi) pv_packed_mma<VB, 2>(a, vc, vs, vz, sm, t0, v_hi);
     __syncthreads();
-    PHASE(5);
 
-    // ---- 4. finish / merge (same protocol as the generic kernel) ------------------------------------
+    // ---- 4. finish / merge --------------------------------------------------------------------------
     float o = (sm.tailred[tid] + sm.tailred[kHeadDim + tid]) + (sm.tailred[2 * kHeadDim + tid] + sm.tailred[3 * kHeadDim + tid]);
     if (t0 < min(t1, a.Tvq)) {                               // each warp left its packed-value partial at its region base
 #pragma unroll
@@ -1090,12 +750,12 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
             o += reinterpret_cast<const float *>(after_scores + w * warp_region_bytes<KB, VB>())[tid];
     }
     __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)h * a.o_sH;
-    if (n_splits == 1) {
+    if (cnt == 1) {
         out[tid] = __float2half_rn(o / l);
         return;
     }
     constexpr int kPart = kHeadDim + 2;
-    float *part = parts + ((int64_t)s * n_splits + split) * kPart;
+    float *part = parts + ((int64_t)(s - n_whole) * cnt + seg) * kPart;          // partials of the cut heads only
     part[tid] = o;
     if (tid == 0) { part[kHeadDim] = m; part[kHeadDim + 1] = l; }
     __syncthreads();
@@ -1103,21 +763,33 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(kvq_att
         // one cumulative device-scope fence after the CTA barrier publishes every thread's partial before the count;
         // the fence after the count orders the merging CTA's reads (ld.cg, from L2) behind the other CTAs' fences
         __threadfence();
-        sm.misc[8] = (atomicAdd(&counters[s], 1u) == (unsigned)(n_splits - 1)) ? 1.f : 0.f;
+        sm.misc[8] = (atomicAdd(&counters[s], 1u) == (unsigned)(cnt - 1)) ? 1.f : 0.f;
         __threadfence();
     }
     __syncthreads();
     if (sm.misc[8] == 0.f) return;
-    const float *base = parts + (int64_t)s * n_splits * kPart;
+    const float *base = parts + (int64_t)(s - n_whole) * cnt * kPart;
     float M = kMaskFloor;
-    for (int i = 0; i < n_splits; ++i) M = fmaxf(M, __ldcg(base + i * kPart + kHeadDim));
+    for (int i = 0; i < cnt; ++i) M = fmaxf(M, __ldcg(base + i * kPart + kHeadDim));
     float L = 0.f, acc = 0.f;
-    for (int i = 0; i < n_splits; ++i) {
+    for (int i = 0; i < cnt; ++i) {
         const float w = __expf(__ldcg(base + i * kPart + kHeadDim) - M);
         L = fmaf(__ldcg(base + i * kPart + kHeadDim + 1), w, L);
         acc = fmaf(__ldcg(base + i * kPart + tid), w, acc);
     }
     out[tid] = __float2half_rn(acc / L);
+    if (tid == 0) counters[s] = 0u;                          // the head is done: its counter is ready for the next launch
+}
+
+// CTA = one segment (see attn_plan.cuh): a whole head, or one of the k pieces of a head that is cut.
+template <int KB, int VB>
+__global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(const __grid_constant__ kvq_attn_args a,
+                                                                     const __grid_constant__ AttnPlan plan,
+                                                                     float *__restrict__ parts,
+                                                                     unsigned int *__restrict__ counters) {
+    int head, t0, t1, seg, cnt;
+    plan_cta(plan, a.T, blockIdx.x, head, t0, t1, seg, cnt);
+    attn_segment<KB, VB>(a, plan.n_scores, head, t0, t1, seg, cnt, plan.n_whole, parts, counters);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1149,26 +821,27 @@ bool mma_path_eligible(const kvq_attn_args &a) {
 }
 
 template <int KB, int VB>
-static int launch_mma(const kvq_attn_args &a, int chunk, int n_splits, float *parts, unsigned int *counters,
+static int launch_mma(const kvq_attn_args &a, const AttnPlan &plan, float *parts, unsigned int *counters,
                       cudaStream_t st) {
-    const int last = a.T - (n_splits - 1) * chunk;            // the last split runs to T
-    int n_scores = (n_splits > 1 && chunk > last) ? chunk : last;
-    n_scores = (n_scores + 31) / 32 * 32;
-    const size_t smem = (size_t)n_scores * 4 + (size_t)kMmaWarps * warp_region_bytes<KB, VB>() +
+    const size_t smem = (size_t)plan.n_scores * 4 + (size_t)kMmaWarps * warp_region_bytes<KB, VB>() +
                         kMmaWarps * kHeadDim * 4 + kHeadDim * 2 + 16 * 4;
-    cudaError_t e = cudaFuncSetAttribute(decode_attn_mma_kernel<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         112 * 1024);
+    static bool attr_set[64] = {};                           // per device: the opt-in is sticky for the process
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return record_cuda_error(e);
-    const int64_t heads = (int64_t)a.B * a.nh;
-    decode_attn_mma_kernel<KB, VB><<<(unsigned)(heads * n_splits), kMmaThreads, smem, st>>>(a, chunk, n_splits, n_scores,
-                                                                                          parts, counters);
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        e = cudaFuncSetAttribute(decode_attn_mma_kernel<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+        if (e != cudaSuccess) return record_cuda_error(e);
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    decode_attn_mma_kernel<KB, VB><<<(unsigned)(plan.n_whole + plan.n_cut * plan.k), kMmaThreads, smem, st>>>(a, plan, parts, counters);
     return check_launch();
 }
 
-int launch_decode_attn_mma(const kvq_attn_args &a, int chunk, int n_splits, float *parts, unsigned int *counters,
+int launch_decode_attn_mma(const kvq_attn_args &a, const AttnPlan &plan, float *parts, unsigned int *counters,
                            cudaStream_t st) {
 #define KVQ_MMA_CASE(KB, VB) \
-    if (a.k_bits == KB && a.v_bits == VB) return launch_mma<KB, VB>(a, chunk, n_splits, parts, counters, st);
+    if (a.k_bits == KB && a.v_bits == VB) return launch_mma<KB, VB>(a, plan, parts, counters, st);
     KVQ_MMA_CASE(4, 4) KVQ_MMA_CASE(4, 2) KVQ_MMA_CASE(4, 1)
     KVQ_MMA_CASE(3, 4) KVQ_MMA_CASE(3, 2) KVQ_MMA_CASE(3, 1)
     KVQ_MMA_CASE(2, 4) KVQ_MMA_CASE(2, 2) KVQ_MMA_CASE(2, 1)
@@ -1177,7 +850,11 @@ int launch_decode_attn_mma(const kvq_attn_args &a, int chunk, int n_splits, floa
     return KVQ_ERR_UNSUPPORTED;
 }
 
+// Plan of the tensor-core kernel for B * nh query heads (one head per segment).
+AttnPlan plan_attn_mma(int T, int k_bits, long long heads) {
+    const int unit = (k_bits == 3) ? 352 : 256;              // one key tile per warp
+    const int max_chunk = (k_bits == 3) ? 8096 : 8192;       // scores held in shared memory
+    return make_attn_plan(T, unit, max_chunk, heads, kSmCount * 3);
+}
+
 }  // namespace kvq
-#ifdef KVQ_PHASE_TIMING
-extern "C" int kvq_debug_phases(unsigned long long *dst) { return (int)cudaMemcpyFromSymbol(dst, kvq::g_phase, sizeof(kvq::g_phase)); }
-#endif

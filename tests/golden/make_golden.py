@@ -146,7 +146,30 @@ def main():
             "oracle_vs_ieee_word_diffs": int((co != n_(ci)).sum()),
             "oracle_vs_fast_word_diffs": int((co != n_(cf)).sum()),
             "oracle_scale_equal_ieee": bool((so == n_(si)).all()),
+            "oracle_scale_diffs_ieee": int((so.view(np.uint16) != n_(si).view(np.uint16)).sum()),
+            "oracle_mn_diffs_ieee": int((mo.view(np.uint16) != n_(mi).view(np.uint16)).sum()),
         }
+        bad = np.argwhere(so.view(np.uint16) != n_(si).view(np.uint16))
+        if len(bad):
+            # keep the evidence: the channel rows holding the first differing groups become a committed vector, and
+            # the report lists the groups with their fp32 extremes and both scale bit patterns
+            ex = []
+            for b_, h_, r_, g_ in bad[:8]:
+                grp = xb[b_, h_, r_, g_ * G:(g_ + 1) * G].astype(np.float32)
+                ex.append({"index": [int(b_), int(h_), int(r_), int(g_)], "min": float(grp.min()), "max": float(grp.max()),
+                           "oracle_scale_bits": int(so.view(np.uint16)[b_, h_, r_, g_]),
+                           "upstream_scale_bits": int(n_(si).view(np.uint16)[b_, h_, r_, g_])})
+            report["tie_stats"][f"b{bits}_g{G}"]["scale_diff_examples"] = ex
+            rows = sorted({(int(b_), int(h_), int(r_)) for b_, h_, r_, _ in bad})[:8]
+            key = f"quant_rows_b{bits}_g{G}_scale"
+            out[key + "_x"] = np.stack([xb[r] for r in rows])[None, None]
+            out[key + "_code"] = np.stack([n_(ci)[r] for r in rows])[None, None]
+            out[key + "_scale"] = np.stack([n_(si)[r] for r in rows])[None, None]
+            out[key + "_mn"] = np.stack([n_(mi)[r] for r in rows])[None, None]
+    if os.path.exists(a.out):                       # regenerating must reproduce every vector already committed
+        prev = np.load(a.out)
+        changed = [k for k in prev.files if k not in out or not np.array_equal(prev[k].view(np.uint8), out[k].view(np.uint8))]
+        report["changed_vs_previous_file"] = changed
     np.savez_compressed(a.out, **out)
     rep = a.report or os.path.join(os.path.dirname(a.out), "ref_report.json")
     with open(rep, "w") as fjs:

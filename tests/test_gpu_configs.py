@@ -58,6 +58,15 @@ def _check_one_sequence(cuda, c, k, v, q, b, kb, vb, G, window):
     assert_attn_parity(kernel, ref, qn)
 
 
+@pytest.mark.parametrize("kb,vb", [(4, 4), (2, 2)])
+def test_config2_layer_full_batch_other_bit_settings(cuda, kb, vb):
+    """The other two bit settings of the Llama-2-7B map at the full batch: K4V4 and K2V2, group 32, window 128."""
+    B, H, T = 64, 32, 4096
+    c, k, v = _layer(cuda, B, H, T, kb, vb, 32, 128)
+    q = _query(cuda, B, H, 112 + kb)
+    _check_one_sequence(cuda, c, k, v, q, 41, kb, vb, 32, 128)
+
+
 def test_config2_layer_full_batch(cuda):
     """Llama-2-7B geometry: batch 64, 32 heads (MHA), context 4096, K3V2 (group 11 / 32), window 128."""
     B, H, T = 64, 32, 4096
@@ -72,9 +81,10 @@ def test_config2_layer_full_batch(cuda):
     assert row_rel(solo.attend(q[17:18]).cpu().numpy(), full[17:18].cpu().numpy()).max() <= 1e-3
 
 
-@pytest.mark.parametrize("kb,vb", [(4, 4), (2, 1)])
+@pytest.mark.parametrize("kb,vb", [(4, 4), (3, 4), (2, 2), (2, 1)])
 def test_config3_layer_gqa_long_context(cuda, kb, vb):
-    """Mistral-7B geometry: batch 8, 32 query / 8 KV heads, context 32768, group 64, window 128."""
+    """Mistral-7B geometry: batch 8, 32 query / 8 KV heads, context 32768, group 64 (11 for 3-bit keys), window 128:
+    every bit setting of its layer map that upstream's format can hold."""
     B, nh, hkv, T = 8, 32, 8, 32768
     c, k, v = _layer(cuda, B, hkv, T, kb, vb, 64, 128)
     q = _query(cuda, B, nh, 103)

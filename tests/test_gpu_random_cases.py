@@ -1,7 +1,8 @@
 """Seeded random configurations of the whole hot path against the oracle: prefill, a run of appends (with the group
 quantizations they trigger), then one fused attention -- every bit width, group size, window, grouped-query ratio,
 context length from one window to 12k tokens, with and without a left-padding mask.  Codes must stay bit-exact
-through the appends; attention is held to the fp32-accumulate statement (2e-3 per row)."""
+through the appends; attention is held to 2e-3 per row twice: score narrowing off against the oracle without
+narrowing, and the default mode (narrowing on) against the oracle with every one of upstream's narrowing points."""
 import random
 
 import numpy as np
@@ -9,7 +10,7 @@ import pytest
 import torch
 
 from oracle.glue import RefLayerCache
-from util import REL_TOL, make_kv, make_q, row_rel
+from util import REL_TOL, assert_close_to_upstream, make_kv, make_q, row_rel
 
 pytestmark = pytest.mark.gpu
 
@@ -52,3 +53,6 @@ def test_random_case(cuda, case):
     got = dut.attend(_t(q, cuda), round_scores=False, attention_mask=_t(mask, cuda)).cpu().numpy()
     assert np.isfinite(got.astype(np.float32)).all()
     assert row_rel(got, want).max() <= REL_TOL
+    want_up = ref.attend(q, ref_rounding=7, attention_mask=mask)
+    got_up = dut.attend(_t(q, cuda), attention_mask=_t(mask, cuda)).cpu().numpy()
+    assert_close_to_upstream(got_up, want_up, want)
