@@ -253,7 +253,29 @@ typedef struct {
     int64_t mask_sB, mask_sH;
     int32_t mask_is_f32;
     int32_t flags;                 /* KVQ_ATTN_* bits; 0 for the behaviour described above */
+    /* Optional cache update fused into the launch (k_new == NULL: none); see "fused decode step" below. */
+    const void *k_new;             /* [B, nh_kv, D] fp16: the step's new key rows, strides kn_sB, kn_sH */
+    const void *v_new;
+    int64_t kn_sB, kn_sH, vn_sB, vn_sH;
+    int32_t k_quant, v_quant;      /* tokens to quantize in this launch: 0, or exactly k_group / v_group */
+    int32_t k_quant_slot, v_quant_slot;   /* ring row of the first of them */
 } kvq_attn_args;
+
+/*
+ * Fused decode step.  Upstream updates the cache and attends in one forward call
+ * (models/modeling_llama_KVmix.py:111-211: cat the new token onto the fp16 tails, quantize a group of the oldest tail
+ * tokens when one is due, then the attention); with k_new / v_new set, kvq_decode_attn does the same in its one
+ * launch.  The caller describes the cache as it is AFTER the update -- T counts the new token, Tkq / Tvq count a group
+ * that becomes packed in this step, kf_start / vf_start are the ring starts after that group left the tails -- and
+ * says what is to be done: the new rows (every reader takes token T-1 from k_new / v_new; one CTA per kv head also
+ * stores them into ring row (kf_start + T-1-Tkq) mod kf_cap, likewise for values), and k_quant / v_quant tokens at
+ * ring rows k_quant_slot.. / v_quant_slot.. to be quantized into packed positions [Tkq - k_quant, Tkq) /
+ * [Tvq - v_quant, Tvq) with the arithmetic of kvq_quant_lastdim (scale_by_division = 0), bit for bit.  kcode, kscale,
+ * kmn, vcode, vscale, vmn, kfull and vfull are written although the struct declares them const.
+ * Served by the tensor-core kernels when exactly one CTA reads a kv head's tokens: nh == nh_kv, or grouped queries
+ * with nh / nh_kv in {2, 4} and group sizes the grouped kernel takes; otherwise KVQ_ERR_UNSUPPORTED is returned before
+ * anything is launched and the caller runs kvq_append_kv / kvq_quant_lastdim / kvq_decode_attn separately.
+ */
 
 /* flags: the counters at the start of the workspace are known to be zero -- cleared once with
  * kvq_decode_attn_workspace_init and since then touched only by this library, whose kernels leave every counter

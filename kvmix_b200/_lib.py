@@ -62,7 +62,9 @@ class AttnArgs(C.Structure):
                 ("vfull", vp), ("vf_sB", i64), ("vf_sH", i64), ("vf_sT", i64),
                 ("vf_cap", i32), ("vf_start", i32),
                 ("workspace", vp), ("workspace_bytes", u64),
-                ("mask", vp), ("mask_sB", i64), ("mask_sH", i64), ("mask_is_f32", i32), ("flags", i32)]
+                ("mask", vp), ("mask_sB", i64), ("mask_sH", i64), ("mask_is_f32", i32), ("flags", i32),
+                ("k_new", vp), ("v_new", vp), ("kn_sB", i64), ("kn_sH", i64), ("vn_sB", i64), ("vn_sH", i64),
+                ("k_quant", i32), ("v_quant", i32), ("k_quant_slot", i32), ("v_quant_slot", i32)]
 
 
 class AttnPlan(C.Structure):

@@ -86,6 +86,7 @@ class KVmixLayerCache:
                              vs.data_ptr(), self.vmn.data_ptr(), vs.stride(0), vs.stride(1), vs.stride(2),
                              vf.data_ptr(), vf.stride(0), vf.stride(1), vf.stride(2), self.v_cap, 0, 0, 0)
         self._ws = {}
+        self._fused = None               # None: not tried yet; False: the library does not fuse this geometry
         self._lib = _lib.lib()
         self.reset()
 
@@ -167,6 +168,15 @@ class KVmixLayerCache:
         self._absorb_ring()
 
     # -- attention -----------------------------------------------------------------------------------
+    def _workspace(self, nh, stream, device):
+        ws = self._ws.get((nh, stream))
+        if ws is None:
+            need = int(self._lib.kvq_decode_attn_workspace_bytes(self.B, nh, self.max_tokens))
+            # zeroed once: the kernels leave the per-head counters at zero, so a step needs no clearing launch
+            # (the layout is fixed for this cache: same B and nh on every call)
+            ws = self._ws[(nh, stream)] = torch.zeros(need, dtype=torch.uint8, device=device)
+        return ws
+
     def attend(self, q, out=None, round_scores=True, attention_mask=None):
         """q: [B,nh,1,D] fp16 -> [B,nh,1,D] fp16 over everything cached (upstream :170-211).  attention_mask:
         optional additive mask over the kv_seq_len cached positions ([B,1,1,T], [B,nh,1,T] or [B,T]; upstream
@@ -181,12 +191,7 @@ class KVmixLayerCache:
         if out is None:
             out = torch.empty((B, nh, 1, D), dtype=torch.float16, device=q.device)
         stream = torch.cuda.current_stream().cuda_stream
-        ws = self._ws.get((nh, stream))
-        if ws is None:
-            need = int(self._lib.kvq_decode_attn_workspace_bytes(B, nh, self.max_tokens))
-            # zeroed once: the kernels leave the per-head counters at zero, so a step needs no clearing launch
-            # (the layout is fixed for this cache: same B and nh on every call)
-            ws = self._ws[(nh, stream)] = torch.zeros(need, dtype=torch.uint8, device=q.device)
+        ws = self._workspace(nh, stream, q.device)
         a = self._att
         a.nh, a.T, a.Tkq, a.Tvq = nh, self.tkq + self.k_len, self.tkq, self.tvq
         a.round_scores = int(bool(round_scores))
@@ -199,9 +204,64 @@ class KVmixLayerCache:
         ops.LAUNCHES[0] += 1
         return out
 
-    def decode_step(self, q, k_new, v_new, out=None, attention_mask=None):
+    def decode_step(self, q, k_new, v_new, out=None, attention_mask=None, round_scores=True):
+        """Upstream's decode branch for one new token (:105-211): cache update, then attention over everything cached.
+        One launch when the library can fuse the update into the attention kernel (one CTA per kv head and segment:
+        MHA, or grouped queries with 2 or 4 query heads per kv head, on the tensor-core kernels); otherwise the ring
+        append, the group quantizers and the attention are launched one after the other (``append`` + ``attend``)."""
+        if self._fused is not False:
+            res = self._decode_step_fused(q, k_new, v_new, out, attention_mask, round_scores)
+            if res is not None:
+                return res
         self.append(k_new, v_new)
-        return self.attend(q, out=out, attention_mask=attention_mask)
+        return self.attend(q, out=out, attention_mask=attention_mask, round_scores=round_scores)
+
+    def _decode_step_fused(self, q, k_new, v_new, out, attention_mask, round_scores):
+        B, nh, M, D = q.shape
+        if M != 1 or B != self.B or D != self.D or not q.is_cuda:
+            raise RuntimeError("decode_step takes q [B, nh, 1, D] on the cache's device")
+        if self.kv_seq_len + 1 > self.max_tokens:
+            raise RuntimeError("cache capacity exceeded")
+        if self.k_len + 1 > self.k_cap or self.v_len + 1 > self.v_cap:
+            raise RuntimeError("fp16 tail larger than the ring capacity (raise max_tail)")
+        if self.tkq + self.k_len != self.tvq + self.v_len:
+            _lib.check(-9)
+        # the state after the update, by upstream's policy (the host mirrors what the kernel is told to do)
+        nk = split_point(self.k_len + 1, self.k_group, self.rk, self.window)
+        nv = split_point(self.v_len + 1, self.v_group, self.rv, self.window)
+        if nk not in (0, self.k_group) or nv not in (0, self.v_group) or nk > self.k_len or nv > self.v_len:
+            return None                                         # more than one group due (a freshly adopted cache): unfused
+        fix = lambda t: t if (t.stride(3) == 1 and t.dtype == torch.float16) else t.to(torch.float16).contiguous()
+        q, k_new, v_new = fix(q), fix(k_new), fix(v_new)
+        if out is None:
+            out = torch.empty((B, nh, 1, D), dtype=torch.float16, device=q.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        ws = self._workspace(nh, stream, q.device)
+        a = self._att
+        a.nh, a.T, a.Tkq, a.Tvq = nh, self.kv_seq_len + 1, self.tkq + nk, self.tvq + nv
+        a.round_scores = int(bool(round_scores))
+        a.q, a.q_sB, a.q_sH = q.data_ptr(), q.stride(0), q.stride(1)
+        a.out, a.o_sB, a.o_sH = out.data_ptr(), out.stride(0), out.stride(1)
+        a.kf_start, a.vf_start = (self.k_start + nk) % self.k_cap, (self.v_start + nv) % self.v_cap
+        a.workspace, a.workspace_bytes, a.flags = ws.data_ptr(), ws.numel(), _lib.ATTN_WORKSPACE_READY
+        a.mask, a.mask_sB, a.mask_sH, a.mask_is_f32 = ops.mask_fields(attention_mask, B, nh, a.T)
+        a.k_new, a.kn_sB, a.kn_sH = k_new.data_ptr(), k_new.stride(0), k_new.stride(1)
+        a.v_new, a.vn_sB, a.vn_sH = v_new.data_ptr(), v_new.stride(0), v_new.stride(1)
+        a.k_quant, a.v_quant, a.k_quant_slot, a.v_quant_slot = nk, nv, self.k_start, self.v_start
+        rc = self._lib.kvq_decode_attn(C.byref(a), C.c_void_p(stream))
+        a.k_new = a.v_new = None
+        a.k_quant = a.v_quant = 0
+        if rc == -11:                                           # this geometry is not served fused: remember and fall back
+            self._fused = False
+            return None
+        _lib.check(rc)
+        ops.LAUNCHES[0] += 1
+        self._fused = True
+        self.tkq, self.tvq = self.tkq + nk, self.tvq + nv
+        self.k_start, self.v_start = a.kf_start, a.vf_start
+        self.k_len, self.v_len = self.k_len + 1 - nk, self.v_len + 1 - nv
+        self.kv_seq_len += 1
+        return out
 
     # -- export in upstream's layout -----------------------------------------------------------------
     def _ring(self, buf, start, n, cap):

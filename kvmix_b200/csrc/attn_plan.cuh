@@ -27,9 +27,12 @@ struct AttnPlan {
 };
 
 constexpr int kSmCount = 148;
-// A CTA costs about this many tokens' worth of time besides the tokens it scores (ring fill, softmax barriers, merge):
-// fitted to B200 timings of 2-bit launches with 256 .. 2048 heads.
-constexpr int kCtaOverheadTokens = 512;
+// A CTA costs about this many tokens' worth of time besides the tokens it scores (launch, ring fill of two phases,
+// softmax barriers, warps that get one key tile fewer than their neighbours, merge).  Measured on B200 with 2-bit
+// keys and values at 4096 tokens: 256 heads take 54 us whole, 60 .. 66 us cut in 2 .. 4 (more CTAs than resident
+// slots), and cutting the 272 heads beyond four full waves of a 2048-head launch costs 1 .. 9 % -- so heads are cut
+// only where the score buffer forces it or where whole heads would leave most slots empty.
+constexpr int kCtaOverheadTokens = 2048;
 constexpr int kMaxCtaRounds = 8;       // cut heads are never spread over more CTAs than this many waves (bounds the workspace)
 
 // heads: number of heads (or head groups); max_chunk: most tokens a segment may hold (score buffer); slots: resident

@@ -282,7 +282,7 @@ int launch_decode_attn_gqa(const kvq_attn_args &a, const AttnPlan &plan, int qhv
 
 // Upper bound, over every shorter context and every kernel, of the partial results (one per query head and segment)
 // a call may hold: the generic kernel's heads x splits; for the tensor-core kernels either what the score buffers
-// force (a segment holds at most 8192 tokens, 2048 / 1760 when four query heads share it) or the planner's own cap of
+// force (a segment holds at most 8192 tokens, 2048 / 2816 when four query heads share it) or the planner's own cap of
 // kMaxCtaRounds waves of CTAs over the cut heads (attn_plan.cuh), whichever is larger.
 static int64_t max_partials_bound(int T, int64_t heads) {
     int64_t n = heads;
@@ -410,6 +410,18 @@ extern "C" int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream) {
 
     const AttnLaunch L = plan_launch(*a);
     if (L.ctas > 2147483647LL) return KVQ_ERR_UNSUPPORTED;
+    if (a->k_new || a->v_new) {                                // fused decode step (see the header)
+        if (!a->k_new || !a->v_new) return KVQ_ERR_NULL;
+        const int n_rep = a->nh / a->nh_kv;
+        if (!L.use_mma || (L.qhv ? n_rep != L.qhv : n_rep != 1)) return KVQ_ERR_UNSUPPORTED;   // one CTA per kv head and segment
+        if (Rk < 1 || Rv < 1) return KVQ_ERR_TOKENS;           // the new token stays in the fp16 tails
+        if ((a->k_quant != 0 && a->k_quant != a->k_group) || (a->v_quant != 0 && a->v_quant != a->v_group)) return KVQ_ERR_TOKENS;
+        if (a->k_quant > a->Tkq || a->v_quant > a->Tvq) return KVQ_ERR_TOKENS;
+        if (a->k_quant && (a->k_quant_slot < 0 || a->k_quant_slot + a->k_quant > a->kf_cap)) return KVQ_ERR_SHAPE;
+        if (a->v_quant && (a->v_quant_slot < 0 || a->v_quant_slot + a->v_quant > a->vf_cap)) return KVQ_ERR_SHAPE;
+        auto bad = [](const void *p, int64_t s0, int64_t s1) { return reinterpret_cast<uintptr_t>(p) % 16 != 0 || s0 % 8 != 0 || s1 % 8 != 0; };
+        if (bad(a->k_new, a->kn_sB, a->kn_sH) || bad(a->v_new, a->vn_sB, a->vn_sH)) return KVQ_ERR_ALIGN;
+    }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     float *parts = nullptr;
     unsigned int *counters = nullptr;

@@ -14,11 +14,12 @@
 // Scores of the four heads sit side by side in shared memory ([4][n]); warp w runs the softmax of head w.
 #include "attn_mma_common.cuh"
 #include "attn_plan.cuh"
+#include "attn_update.cuh"
 
 namespace kvq {
 
 constexpr int kQH = 4;                  // query-head slots per CTA
-constexpr int kGqaMaxChunk = 2048;      // tokens per segment: 4 x 2048 fp32 scores
+constexpr int kGqaMaxChunk = 2048;      // tokens per segment: 4 x 2048 fp32 scores (3072 fit too but measured 10 % slower)
 constexpr int kGqaTailOff = 2048;       // per-warp region: [value ring | operand tiles (2 KB) | fp16-tail partial (2 KB)]
 
 struct GqaSmem {
@@ -57,8 +58,8 @@ __device__ __forceinline__ uint32_t hilo(__half2 q, __half2 s, uint32_t neg_mask
 
 // ---------------------------------------------------------------------------------------------
 // fp16 key tail for tokens [lo, t1): 16-token tiles straight from global memory; B column n = query head n.
-__device__ __forceinline__ void gqa_qk_tail(const kvq_attn_args &a, const __half *kf, const GqaSmem &sm, int t0, int lo,
-                                            int t1) {
+__device__ __forceinline__ void gqa_qk_tail(const kvq_attn_args &a, const __half *kf, int b, int hk, const GqaSmem &sm,
+                                            int t0, int lo, int t1) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
     uint4 qf[4];
 #pragma unroll
@@ -67,10 +68,8 @@ __device__ __forceinline__ void gqa_qk_tail(const kvq_attn_args &a, const __half
     const int n_tiles = (t1 - lo + 15) / 16;
     for (int tile = warp; tile < n_tiles; tile += kMmaWarps) {
         const int ta = lo + 16 * tile + g, tb = ta + 8;
-        int sa = a.kf_start + (min(ta, t1 - 1) - a.Tkq), sb = a.kf_start + (min(tb, t1 - 1) - a.Tkq);
-        if (sa >= a.kf_cap) sa -= a.kf_cap;
-        if (sb >= a.kf_cap) sb -= a.kf_cap;
-        const __half *pa = kf + (int64_t)sa * a.kf_sT + 8 * tig, *pb = kf + (int64_t)sb * a.kf_sT + 8 * tig;
+        const __half *pa = k_tail_row(a, kf, b, hk, min(ta, t1 - 1)) + 8 * tig;
+        const __half *pb = k_tail_row(a, kf, b, hk, min(tb, t1 - 1)) + 8 * tig;
         uint4 ra[4], rb[4];
 #pragma unroll
         for (int S = 0; S < 4; ++S) {
@@ -101,7 +100,7 @@ __device__ __forceinline__ void gqa_qk_tail(const kvq_attn_args &a, const __half
 template <int KB>
 __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int32_t *kc, const __half *ks,
                                               const __half *kz, const GqaSmem &sm, int t0, int hi, const __half *kf,
-                                              int tail_lo, int t1) {
+                                              int tail_lo, int t1, int b, int hk) {
     using G = KGeom<KB>;
     using F = Fields<KB>;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
@@ -111,7 +110,7 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
     const int my_tiles = (n_tiles - warp + kMmaWarps - 1) / kMmaWarps;
     if (my_tiles <= 0) {
         __syncthreads();                                       // q is in shared memory
-        if (tail_lo < t1) gqa_qk_tail(a, kf, sm, t0, tail_lo, t1);
+        if (tail_lo < t1) gqa_qk_tail(a, kf, b, hk, sm, t0, tail_lo, t1);
         return;
     }
     const int kc_sD = (int)a.kc_sD, ks_sD = (int)a.ks_sD;
@@ -178,7 +177,7 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
     issue_stage(tb_cur, ok_cur, 2);
     cp_async_commit();
     __syncthreads();                                           // q is in shared memory (stored by the caller without a barrier)
-    if (tail_lo < t1) gqa_qk_tail(a, kf, sm, t0, tail_lo, t1);
+    if (tail_lo < t1) gqa_qk_tail(a, kf, b, hk, sm, t0, tail_lo, t1);
 
     const uint32_t ones = 0x3c003c00u;
     for (int j = 0; j < my_tiles; ++j) {
@@ -188,9 +187,15 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
         const bool ok_nxt = have_next && (wcol_cur + tile_words < n_words);
 
         const uint32_t szbuf = (j & 1) ? SZB : 0u;
-        float acc[NACC][4], accz[4] = {0.f, 0.f, 0.f, 0.f};
+        // groups of this tile that hold tokens below hi: operands of the others are never formed (their scale/zero
+        // words lie beyond the packed prefix and may hold anything, and 0 * NaN would poison a shared accumulator)
+        const int nvg = min(ngw, (hi - tile0 + Gk - 1) / Gk);
+        // the zero-term MMAs rotate over four accumulators so that consecutive ones do not wait for each other
+        float acc[NACC][4], accz[4][4];
 #pragma unroll
         for (int m = 0; m < NACC; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) accz[m][0] = accz[m][1] = accz[m][2] = accz[m][3] = 0.f;
 
 #pragma unroll
         for (int st = 0; st < G::NSTAGE; ++st) {
@@ -224,6 +229,7 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
 #pragma unroll
                         for (int u = 0; u < 2; ++u) {
                             const int jw = 2 * jp + u;
+                            if (jw >= nvg) continue;
                             const uint32_t psel = u ? 0x7632u : 0x5410u;
                             const __half2 s01 = as_h2(prmt(sA, sB, psel)), s89 = as_h2(prmt(sC, sD, psel));
                             const __half2 z01 = as_h2(prmt(zA, zB, psel)), z89 = as_h2(prmt(zC, zD, psel));
@@ -232,7 +238,7 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
                                      prmt(a_hi, b_hi, sel0) & msk0, prmt(a_hi, b_hi, sel1) & msk1,
                                      hilo(q01, s01, neg_mask), hilo(q89, s89, neg_mask));
                             const uint32_t row1 = (g == jw) ? ones : 0u;
-                            mma16816(accz, row1, 0u, row1, 0u, hilo(q01, z01, neg_mask), hilo(q89, z89, neg_mask));
+                            mma16816(accz[jw & 3], row1, 0u, row1, 0u, hilo(q01, z01, neg_mask), hilo(q89, z89, neg_mask));
                         }
                     }
                 } else {
@@ -242,14 +248,14 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
                     uint32_t b[4][2];
 #pragma unroll
                     for (int jk = 0; jk < 4; ++jk) {
-                        if (jk < ngw) {
+                        if (jk < nvg) {
                             const uint32_t psel = (jk & 1) ? 0x7632u : 0x5410u;
                             const uint32_t a0 = (jk & 2) ? sA.y : sA.x, a1 = (jk & 2) ? sB.y : sB.x, a2 = (jk & 2) ? sC.y : sC.x, a3 = (jk & 2) ? sD.y : sD.x;
                             const uint32_t c0 = (jk & 2) ? zA.y : zA.x, c1 = (jk & 2) ? zB.y : zB.x, c2 = (jk & 2) ? zC.y : zC.x, c3 = (jk & 2) ? zD.y : zD.x;
                             b[jk][0] = hilo(q01, as_h2(prmt(a0, a1, psel)), neg_mask);
                             b[jk][1] = hilo(q89, as_h2(prmt(a2, a3, psel)), neg_mask);
                             const uint32_t row1 = (g == jk) ? ones : 0u;
-                            mma16816(accz, row1, 0u, row1, 0u, hilo(q01, as_h2(prmt(c0, c1, psel)), neg_mask),
+                            mma16816(accz[jk], row1, 0u, row1, 0u, hilo(q01, as_h2(prmt(c0, c1, psel)), neg_mask),
                                      hilo(q89, as_h2(prmt(c2, c3, psel)), neg_mask));
                         } else {
                             b[jk][0] = b[jk][1] = 0u;
@@ -282,7 +288,8 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
         }
 
         // ---- epilogue: lane (g, tig) holds, per accumulator, row g / g + 8 of head tig as (hi, lo) ------------
-        const float zsum = accz[0] + accz[1];                  // row g = group g of the tile: its zero term for head tig
+        // row g = group g of the tile: its zero term for head tig (hi + lo columns, summed over the rotating accumulators)
+        const float zsum = ((accz[0][0] + accz[0][1]) + (accz[1][0] + accz[1][1])) + ((accz[2][0] + accz[2][1]) + (accz[3][0] + accz[3][1]));
         float *dst_h = sm.scores + tig * sm.n_scores - t0;
         if constexpr (KB == 3) {
 #pragma unroll
@@ -399,7 +406,7 @@ __device__ __forceinline__ void gqa_pv_packed(const kvq_attn_args &a, const int3
         src_sz += sz_step;
     };
 
-    float acc[8][4], accz[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[8][4], accz[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};    // ones-MMAs alternate between two accumulators
 #pragma unroll
     for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
     const uint32_t ones = 0x3c003c00u;
@@ -414,9 +421,10 @@ __device__ __forceinline__ void gqa_pv_packed(const kvq_attn_args &a, const int3
             sum[m][1] += acc[m][2];
             acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
         }
-        sumz[0] += accz[0];
-        sumz[1] += accz[1];
-        accz[0] = accz[1] = accz[2] = accz[3] = 0.f;
+        sumz[0] += accz[0][0] + accz[1][0];
+        sumz[1] += accz[0][1] + accz[1][1];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) accz[u][0] = accz[u][1] = accz[u][2] = accz[u][3] = 0.f;
     };
 
     if (MODE != 2) {
@@ -463,7 +471,7 @@ __device__ __forceinline__ void gqa_pv_packed(const kvq_attn_args &a, const int3
                     b[jv][0] = lds32(pb_rd + jv * 512 + (8 * h2) * 32);
                     b[jv][1] = lds32(pb_rd + jv * 512 + (8 * h2 + 4) * 32);
                     const uint32_t row1 = (g == jv) ? ones : 0u;    // sums of group jv land in row jv
-                    mma16816(accz, row1, 0u, row1, 0u, b[jv][0], b[jv][1]);
+                    mma16816(accz[jv & 1], row1, 0u, row1, 0u, b[jv][0], b[jv][1]);
                 } else {
                     b[jv][0] = b[jv][1] = 0u;
                 }
@@ -544,6 +552,7 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, int n_scores
     const int n_rep = a.nh / a.nh_kv, nq = n_rep / qhv;                // quads per kv head
     const int b = s / (a.nh_kv * nq), hk = (s / nq) % a.nh_kv, h_first = hk * n_rep + (s % nq) * qhv;
 
+    fused_cache_update<KB, VB>(a, b, hk, t0, t1, tid);        // the step's own cache update, when the caller fused it in
     // q of the quad (head slots beyond qhv repeat the last head: their columns are computed and dropped)
     {
         const int hs = min(tid >> 5, qhv - 1);                          // warp w stores head slot w
@@ -559,10 +568,10 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, int n_scores
             const int32_t *kc = a.kcode + (int64_t)b * a.kc_sB + (int64_t)hk * a.kc_sH;
             const __half *ks = static_cast<const __half *>(a.kscale) + (int64_t)b * a.ks_sB + (int64_t)hk * a.ks_sH;
             const __half *kz = static_cast<const __half *>(a.kmn) + (int64_t)b * a.ks_sB + (int64_t)hk * a.ks_sH;
-            gqa_qk_packed<KB>(a, kc, ks, kz, sm, t0, hi, kf, max(t0, a.Tkq), t1);
+            gqa_qk_packed<KB>(a, kc, ks, kz, sm, t0, hi, kf, max(t0, a.Tkq), t1, b, hk);
         } else {
             __syncthreads();
-            if (t0 < t1) gqa_qk_tail(a, kf, sm, t0, t0, t1);
+            if (t0 < t1) gqa_qk_tail(a, kf, b, hk, sm, t0, t0, t1);
         }
     }
     const int32_t *vc = a.vcode + (int64_t)b * a.vc_sB + (int64_t)hk * a.vc_sH;
@@ -583,9 +592,7 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, int n_scores
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const int t = base + tl + 8 * j;
-            int s0 = a.vf_start + (t - a.Tvq);
-            if (s0 >= a.vf_cap) s0 -= a.vf_cap;
-            vt[j] = (t < t1) ? __ldg(reinterpret_cast<const uint4 *>(vf + (int64_t)s0 * a.vf_sT) + co) : make_uint4(0u, 0u, 0u, 0u);
+            vt[j] = (t < t1) ? __ldg(reinterpret_cast<const uint4 *>(v_tail_row(a, vf, b, hk, t)) + co) : make_uint4(0u, 0u, 0u, 0u);
         }
     };
     if (v_lo < t1) load_tail_round(v_lo);
@@ -744,7 +751,7 @@ int gqa_heads_per_cta(const kvq_attn_args &a) {
 
 AttnPlan plan_attn_gqa(int T, int k_bits, long long head_groups) {
     const int unit = (k_bits == 3) ? 352 : 256;
-    const int max_chunk = (k_bits == 3) ? 1760 : kGqaMaxChunk;
+    const int max_chunk = (k_bits == 3) ? 2816 : kGqaMaxChunk;     // whole units of 352 / 256 tokens
     return make_attn_plan(T, unit, max_chunk, head_groups, kSmCount * 2);
 }
 

@@ -26,6 +26,7 @@
 // memory; the softmax, the optional additive mask and the fp16 value tail run on the CUDA cores.
 #include "attn_mma_common.cuh"
 #include "attn_plan.cuh"
+#include "attn_update.cuh"
 
 namespace kvq {
 
@@ -41,15 +42,15 @@ struct MmaSmem {
 // q . K^T over packed keys for tokens [t0, hi) (t0 is a multiple of 1024, or 352 for 3-bit keys).
 // Scores (already multiplied by softmax_scale) go to sm.scores[t - t0].  Warps work independently:
 // warp w takes warp tiles w, w+4, ... and streams their code words through its own ring.
-__device__ __forceinline__ void qk_tail_mma(const kvq_attn_args &a, const __half *kf, const MmaSmem &sm, int t0,
-                                            int lo, int t1);
+__device__ __forceinline__ void qk_tail_mma(const kvq_attn_args &a, const __half *kf, int b, int hk, const MmaSmem &sm,
+                                            int t0, int lo, int t1);
 
 // If the split also holds fp16 tail keys (tail_lo < t1) they are scored right after the first code stages
 // have been issued, so the tail's global-load latency overlaps the ring fill.
 template <int KB>
 __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int32_t *kc, const __half *ks,
                                               const __half *kz, const MmaSmem &sm, int t0, int hi,
-                                              const __half *kf, int tail_lo, int t1) {
+                                              const __half *kf, int tail_lo, int t1, int b, int hk) {
     using G = KGeom<KB>;
     using F = Fields<KB>;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
@@ -59,7 +60,7 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     const int my_tiles = (n_tiles - warp + kMmaWarps - 1) / kMmaWarps;   // tiles warp, warp+4, ...
     if (my_tiles <= 0) {
         __syncthreads();                                       // q is in shared memory (see below)
-        if (tail_lo < t1) qk_tail_mma(a, kf, sm, t0, tail_lo, t1);
+        if (tail_lo < t1) qk_tail_mma(a, kf, b, hk, sm, t0, tail_lo, t1);
         return;
     }
 
@@ -125,7 +126,7 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     // The caller stored q to shared memory just before this call without a barrier, so that the first code stages
     // are in flight while q arrives; every warp passes exactly one barrier here before anything reads q.
     __syncthreads();
-    if (tail_lo < t1) qk_tail_mma(a, kf, sm, t0, tail_lo, t1);
+    if (tail_lo < t1) qk_tail_mma(a, kf, b, hk, sm, t0, tail_lo, t1);
 
     const uint32_t ones = 0x3c003c00u;
     for (int j = 0; j < my_tiles; ++j) {
@@ -567,8 +568,8 @@ __device__ __forceinline__ void pv_packed_mma(const kvq_attn_args &a, const int3
 // q . K^T over the fp16 tail for tokens [lo, t1): 16-token tiles on the tensor core, straight from
 // global memory (row g and g+8 of a tile per lane-octet, 16-byte loads of 8 channels; the k axis is
 // permuted identically in the q fragments).  Every B column carries q, so each lane sees its rows' sums.
-__device__ __forceinline__ void qk_tail_mma(const kvq_attn_args &a, const __half *kf, const MmaSmem &sm, int t0,
-                                            int lo, int t1) {
+__device__ __forceinline__ void qk_tail_mma(const kvq_attn_args &a, const __half *kf, int b, int hk, const MmaSmem &sm,
+                                            int t0, int lo, int t1) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
     uint4 qf[4];
 #pragma unroll
@@ -576,10 +577,8 @@ __device__ __forceinline__ void qk_tail_mma(const kvq_attn_args &a, const __half
     const int n_tiles = (t1 - lo + 15) / 16;
     for (int tile = warp; tile < n_tiles; tile += kMmaWarps) {
         const int ta = lo + 16 * tile + g, tb = ta + 8;
-        int sa = a.kf_start + (min(ta, t1 - 1) - a.Tkq), sb = a.kf_start + (min(tb, t1 - 1) - a.Tkq);
-        if (sa >= a.kf_cap) sa -= a.kf_cap;
-        if (sb >= a.kf_cap) sb -= a.kf_cap;
-        const __half *pa = kf + (int64_t)sa * a.kf_sT + 8 * tig, *pb = kf + (int64_t)sb * a.kf_sT + 8 * tig;
+        const __half *pa = k_tail_row(a, kf, b, hk, min(ta, t1 - 1)) + 8 * tig;
+        const __half *pb = k_tail_row(a, kf, b, hk, min(tb, t1 - 1)) + 8 * tig;
         uint4 ra[4], rb[4];
 #pragma unroll
         for (int S = 0; S < 4; ++S) {
@@ -625,6 +624,7 @@ __device__ __forceinline__ void attn_segment(const kvq_attn_args &a, int n_score
     // neighbouring units of work, so the cache is fetched from HBM once and re-read from L2
     const int hk = h / (a.nh / a.nh_kv);
 
+    fused_cache_update<KB, VB>(a, b, hk, t0, t1, tid);        // the step's own cache update, when the caller fused it in
     const __half *q = static_cast<const __half *>(a.q) + (int64_t)b * a.q_sB + (int64_t)h * a.q_sH;
     if (tid < kHeadDim) sm.q[tid] = q[tid];
     for (int i = tid; i < kMmaWarps * kHeadDim; i += kMmaThreads) sm.tailred[i] = 0.f;
@@ -637,11 +637,11 @@ __device__ __forceinline__ void attn_segment(const kvq_attn_args &a, int n_score
             const __half *ks = static_cast<const __half *>(a.kscale) + (int64_t)b * a.ks_sB + (int64_t)hk * a.ks_sH;
             const __half *kz = static_cast<const __half *>(a.kmn) + (int64_t)b * a.ks_sB + (int64_t)hk * a.ks_sH;
             const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)hk * a.kf_sH;
-            qk_packed_mma<KB>(a, kc, ks, kz, sm, t0, hi, kf, max(t0, a.Tkq), t1);
+            qk_packed_mma<KB>(a, kc, ks, kz, sm, t0, hi, kf, max(t0, a.Tkq), t1, b, hk);
         } else {
             __syncthreads();                                   // q is in shared memory
             const __half *kf = static_cast<const __half *>(a.kfull) + (int64_t)b * a.kf_sB + (int64_t)hk * a.kf_sH;
-            if (t0 < t1) qk_tail_mma(a, kf, sm, t0, t0, t1);
+            if (t0 < t1) qk_tail_mma(a, kf, b, hk, sm, t0, t0, t1);
         }
     }
     const int32_t *vc = a.vcode + (int64_t)b * a.vc_sB + (int64_t)hk * a.vc_sH;
@@ -664,9 +664,7 @@ __device__ __forceinline__ void attn_segment(const kvq_attn_args &a, int n_score
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const int t = base + tl + 8 * j;
-            int s0 = a.vf_start + (t - a.Tvq);
-            if (s0 >= a.vf_cap) s0 -= a.vf_cap;
-            vt[j] = (t < t1) ? __ldg(reinterpret_cast<const uint4 *>(vf + (int64_t)s0 * a.vf_sT) + co) : make_uint4(0u, 0u, 0u, 0u);
+            vt[j] = (t < t1) ? __ldg(reinterpret_cast<const uint4 *>(v_tail_row(a, vf, b, hk, t)) + co) : make_uint4(0u, 0u, 0u, 0u);
         }
     };
     if (v_lo < t1) load_tail_round(v_lo);

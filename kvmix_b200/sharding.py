@@ -41,15 +41,38 @@ def shard_kv_heads(n_heads, n_kv_heads, world, rank):
 
 
 def all_gather_heads(out_local, group=None):
-    """[B, nh_local, 1, D] on every rank -> [B, nh, 1, D], heads in rank order."""
+    """[B, nh_local, 1, D] on every rank -> [B, nh, 1, D], heads in rank order (allocates; see HeadGather)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world == 1:
         return out_local
-    B, nhl, one, D = out_local.shape
-    flat = out_local.transpose(0, 1).contiguous()                 # [nh_local, B, 1, D]: gather along dim 0
-    full = torch.empty((world * nhl, B, one, D), dtype=out_local.dtype, device=out_local.device)
-    dist.all_gather_into_tensor(full, flat, group=group)
-    return full.transpose(0, 1).contiguous()
+    return HeadGather(out_local.shape[0], out_local.shape[1], out_local.shape[3], out_local.dtype, out_local.device,
+                      group)(out_local)
+
+
+class HeadGather:
+    """The per-layer exchange of the kv-head-sharded decode step with everything preallocated: one
+    ``all_gather_into_tensor`` per call into a buffer made once.  With one sequence per rank (the long-context
+    configuration) the rank-major gather layout [world, 1, nh_local, 1, D] already *is* [1, nh, 1, D], so the result is
+    a view; with B > 1 one strided copy reorders it."""
+
+    def __init__(self, batch, nh_local, head_dim, dtype, device, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.B, self.nhl, self.D = batch, nh_local, head_dim
+        self.full = torch.empty((self.world, batch, nh_local, 1, head_dim), dtype=dtype, device=device)
+        self.out = self.full.view(1, self.world * nh_local, 1, head_dim) if batch == 1 else \
+            torch.empty((batch, self.world * nh_local, 1, head_dim), dtype=dtype, device=device)
+
+    def __call__(self, out_local):
+        if self.world == 1:
+            return out_local
+        if not out_local.is_contiguous():
+            out_local = out_local.contiguous()
+        dist.all_gather_into_tensor(self.full.view(self.world * self.B, self.nhl, 1, self.D), out_local, group=self.group)
+        if self.B == 1:
+            return self.out
+        self.out.view(self.B, self.world, self.nhl, 1, self.D).copy_(self.full.permute(1, 0, 2, 3, 4))
+        return self.out
 
 
 def max_over_ranks(value, device, group=None):

@@ -48,6 +48,12 @@ def lib():
     return _lib
 
 
+def set_threads(n):
+    """Use n OpenMP threads in the C kernels from now on (overrides OMP_NUM_THREADS); returns the count in effect."""
+    lib().orc_set_threads(int(n))
+    return int(lib().orc_max_threads())
+
+
 def _p(a):
     return a.ctypes.data_as(ctypes.c_void_p)
 

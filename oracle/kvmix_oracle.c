@@ -36,6 +36,17 @@ static inline h16 f2h(float f) { _Float16 x = (_Float16)f; h16 h; memcpy(&h, &x,
 
 int orc_features_per_int(int bits) { return bits == 3 ? 11 : 32 / bits; }
 
+/* Thread control for the timed CPU baseline: launchers such as torchrun export OMP_NUM_THREADS=1, which would
+ * silently turn the "all host cores" figure into a one-core one. */
+#ifdef _OPENMP
+#include <omp.h>
+void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int orc_max_threads(void) { return omp_get_max_threads(); }
+#else
+void orc_set_threads(int n) { (void)n; }
+int orc_max_threads(void) { return 1; }
+#endif
+
 /* Argument rules of quantize_pack_last_dim_cuda, quant_cuda/csrc/quantization_cuda.cu:637-653,687.
  * Returns 0 when legal, a negative code naming the violated TORCH_CHECK otherwise. */
 int orc_quant_check(int64_t S, int G, int bits) {

@@ -104,5 +104,4 @@ def upstream_step(ext, st, q, k_new, v_new, kb, vb, Gk, Gv, policy, n_rep, mask)
                                    rep(st["vm"], n_rep), vb)
         out_f = torch.matmul(w[:, :, :, -r:], rep(st["vfull"], n_rep))
         out = out_q + out_f
-    torch.cuda.synchronize()      # the extension's GEMV runs on the legacy default stream
-    return out
+    return out                    # (the extension's GEMV runs on the legacy default stream: callers synchronise)

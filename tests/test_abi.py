@@ -129,7 +129,7 @@ def test_split_plan_invariants_and_workspace_bound():
                     groups = heads // p.heads_per_cta
                     assert p.unit == (352 if kb == 3 else 256) and p.units_per_head == -(-T // p.unit)
                     assert p.n_whole + p.n_cut == groups and p.n_ctas == p.n_whole + p.n_cut * p.segments
-                    slots, cap = (148 * 2, 1760 if kb == 3 else 2048) if grouped else (148 * 3, 8096 if kb == 3 else 8192)
+                    slots, cap = (148 * 2, 2816 if kb == 3 else 2048) if grouped else (148 * 3, 8096 if kb == 3 else 8192)
                     assert p.n_whole % slots == 0 and p.max_segment_tokens <= cap
                     assert (p.segments - 1) * p.segment_units < p.units_per_head <= p.segments * p.segment_units
                     if p.n_ctas <= 40000:                                    # walk the small and medium plans fully
@@ -147,12 +147,12 @@ def test_split_plan_invariants_and_workspace_bound():
 
 
 def test_split_plan_prefers_one_split_for_full_grids():
-    p = _plan(64, 32, 4119, 2, 1)                            # 2048 heads: four waves of whole heads, the rest cut
-    assert (p.n_whole, p.n_cut) == (1776, 272) and p.segments > 1 and p.max_segment_tokens == 4128
-    p = _plan(8, 32, 4096, 2, 1)                             # 256 heads for 444 slots: cut so that two rounds fill them
-    assert (p.n_whole, p.n_cut) == (0, 256) and p.segments == 3
-    p = _plan(1, 32, 1024, 4, 1)
-    assert (p.n_whole, p.n_cut) == (0, 32)
+    p = _plan(64, 32, 4119, 2, 1)                            # 2048 heads of 4119 tokens: one CTA per head
+    assert (p.n_whole, p.n_cut, p.segments) == (1776, 272, 1) and p.max_segment_tokens == 4128
+    p = _plan(8, 32, 4096, 2, 1)                             # 256 heads for 444 slots: cutting would need a second round
+    assert (p.n_whole, p.n_cut, p.segments) == (0, 256, 1)
+    p = _plan(1, 32, 4096, 2, 1)                             # 32 heads: cut, the slots are mostly empty otherwise
+    assert p.segments > 1 and p.n_ctas <= 444
     assert _plan(1, 32, 131072, 4, 1).segments > 8           # one long sequence: many segments per head
     p = _plan(8, 32, 32768, 2, 1, nh_kv=8, G=64)             # grouped queries: 64 head groups of 4 query heads
     assert (p.kernel, p.heads_per_cta, p.n_whole + p.n_cut) == (2, 4, 64) and p.max_segment_tokens <= 2048
