@@ -153,6 +153,50 @@ typedef struct {
 int kvq_append_kv(const kvq_append_args *a, kvq_stream_t stream);
 
 /*
+ * Prompt prefill straight from the projections.
+ * Replaces the quantization half of upstream's no-cache branch (models/modeling_llama_KVmix.py:213-254) together with
+ * what precedes it there: the rotary embedding of the keys (:103, apply_rotary_pos_emb), the slice + .contiguous() +
+ * .transpose(2, 3).contiguous() copies of the keys (:225-231) and the slice copies of the tails (:226, :243).
+ *   k, v      the k_proj / v_proj outputs of the prompt, fp16, element (b, t, h, d) at k + b*k_sB + t*k_sT + h*k_sH + d
+ *             (e.g. [B, L, Hkv*D] as the projection writes it: k_sT = Hkv*D, k_sH = D; [B, Hkv, L, D] works alike)
+ *   cos, sin  rotary tables, fp16, element (b, t, d) at cos + b*r_sB + t*r_sT + d (r_sB = 0 for one table shared by
+ *             the batch); NULL when the keys arrive rotated.  Rotation is the rotate_half form with fp16 rounding of
+ *             each product and of the sum, i.e. bit-identical to (k * cos) + (rotate_half(k) * sin) on fp16 tensors.
+ *   nk, nv    tokens to quantize (upstream's split points: multiples of k_group / v_group); keys [0, nk) are rotated
+ *             and quantized per channel over groups of k_group tokens into kcode / kscale / kmn, values [0, nv) per
+ *             token over groups of v_group channels, exactly as kvq_quant_lastdim (scale_by_division = 0) would;
+ *             the remaining tokens go, rotated, to rows 0.. of the fp16 tails kfull / vfull.
+ * Three launches (key quantizer, value quantizer, tails), no temporary tensors.  D must be 128.
+ */
+typedef struct {
+    const void *k;
+    const void *v;
+    int64_t k_sB, k_sT, k_sH, v_sB, v_sT, v_sH;
+    const void *cos;
+    const void *sin;
+    int64_t r_sB, r_sT;
+    int32_t B, Hkv, L, D;
+    int32_t nk, nv;
+    int32_t k_bits, k_group, v_bits, v_group;
+    int32_t *kcode;
+    int64_t kc_sB, kc_sH, kc_sD;
+    void *kscale;
+    void *kmn;
+    int64_t ks_sB, ks_sH, ks_sD;
+    int32_t *vcode;
+    int64_t vc_sB, vc_sH, vc_sT;
+    void *vscale;
+    void *vmn;
+    int64_t vs_sB, vs_sH, vs_sT;
+    void *kfull;
+    int64_t kf_sB, kf_sH, kf_sT;
+    void *vfull;
+    int64_t vf_sB, vf_sH, vf_sT;
+} kvq_prefill_args;
+
+int kvq_prefill(const kvq_prefill_args *a, kvq_stream_t stream);
+
+/*
  * Dequantising mat-vec, M = 1.
  * Replaces quantized_gemm, upstream quant_cuda/csrc/dequantization_gemv_cuda.cu:127-248 (kernel
  * :7-124), reading the caller's layout directly (upstream first transposes codes, scales and
@@ -221,6 +265,7 @@ int kvq_gemv(const kvq_gemv_args *a, kvq_stream_t stream);
  * several CTAs and one counter per query head).  The call zeroes the counters itself unless flags says they are
  * ready; concurrent calls must not share a workspace.
  */
+#define KVQ_MAX_PEERS 8
 typedef struct {
     int32_t B, nh, nh_kv, D;
     int32_t T, Tkq, Tvq;
@@ -259,6 +304,11 @@ typedef struct {
     int64_t kn_sB, kn_sH, vn_sB, vn_sH;
     int32_t k_quant, v_quant;      /* tokens to quantize in this launch: 0, or exactly k_group / v_group */
     int32_t k_quant_slot, v_quant_slot;   /* ring row of the first of them */
+    /* Optional exchange fused into the launch (n_peers == 0: none); see "head-sharded exchange" below. */
+    int32_t n_peers, peer_head0;
+    void *peer_out[KVQ_MAX_PEERS];         /* [B, nh_total, D] fp16 gather buffer of every rank, strides peer_sB, peer_sH */
+    uint32_t *peer_flag[KVQ_MAX_PEERS];    /* one arrival counter per rank */
+    int64_t peer_sB, peer_sH;
 } kvq_attn_args;
 
 /*
@@ -277,10 +327,29 @@ typedef struct {
  * anything is launched and the caller runs kvq_append_kv / kvq_quant_lastdim / kvq_decode_attn separately.
  */
 
+/*
+ * Head-sharded exchange.  When the KV heads of a long sequence are split across the GPUs of a node, every rank needs
+ * all ranks' attention outputs before the output projection (no upstream counterpart: upstream is single-GPU).  With
+ * n_peers > 0 the CTA that finishes a query head stores its row, besides `out`, straight into every rank's gather
+ * buffer -- peer_out[p] + b*peer_sB + (peer_head0 + h)*peer_sH, plain stores through peer-mapped pointers (NVLink),
+ * no multicast -- and then adds the number of heads it wrote to every rank's arrival counter peer_flag[p] with a
+ * system-scope release.  A consumer waits for its counter with kvq_peer_wait.  peer_out / peer_flag include this
+ * rank's own buffer and counter.  KVQ_MAX_PEERS ranks at most.
+ */
+
 /* flags: the counters at the start of the workspace are known to be zero -- cleared once with
  * kvq_decode_attn_workspace_init and since then touched only by this library, whose kernels leave every counter
  * they use at zero.  The call then skips its own clearing (one memset node less per decode step). */
 #define KVQ_ATTN_WORKSPACE_READY 1
+
+/*
+ * Waits (on `stream`, on the device) until *counter has reached `expected` arrivals (counters only grow; the
+ * comparison is wrap-safe), polling at most max_polls times with a short sleep between polls -- about 1 us each, so
+ * 1000000 is roughly a second.  If the count does not arrive, the kernel gives up, stores 1 into status[0] and the
+ * value it last saw into status[1], and returns; the context stays usable and the host decides what to do (a peer that
+ * died, a shard that was never launched).  status must be device memory holding two int32, zeroed by the caller.
+ */
+int kvq_peer_wait(const uint32_t *counter, uint32_t expected, uint32_t max_polls, int32_t *status, kvq_stream_t stream);
 
 uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32_t T);
 /* Clears the counters of a workspace for B * nh query heads (asynchronously, on `stream`). */

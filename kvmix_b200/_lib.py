@@ -64,7 +64,22 @@ class AttnArgs(C.Structure):
                 ("workspace", vp), ("workspace_bytes", u64),
                 ("mask", vp), ("mask_sB", i64), ("mask_sH", i64), ("mask_is_f32", i32), ("flags", i32),
                 ("k_new", vp), ("v_new", vp), ("kn_sB", i64), ("kn_sH", i64), ("vn_sB", i64), ("vn_sH", i64),
-                ("k_quant", i32), ("v_quant", i32), ("k_quant_slot", i32), ("v_quant_slot", i32)]
+                ("k_quant", i32), ("v_quant", i32), ("k_quant_slot", i32), ("v_quant_slot", i32),
+                ("n_peers", i32), ("peer_head0", i32), ("peer_out", vp * 8), ("peer_flag", vp * 8),
+                ("peer_sB", i64), ("peer_sH", i64)]
+
+
+class PrefillArgs(C.Structure):
+    _fields_ = [("k", vp), ("v", vp), ("k_sB", i64), ("k_sT", i64), ("k_sH", i64), ("v_sB", i64), ("v_sT", i64), ("v_sH", i64),
+                ("cos", vp), ("sin", vp), ("r_sB", i64), ("r_sT", i64),
+                ("B", i32), ("Hkv", i32), ("L", i32), ("D", i32), ("nk", i32), ("nv", i32),
+                ("k_bits", i32), ("k_group", i32), ("v_bits", i32), ("v_group", i32),
+                ("kcode", vp), ("kc_sB", i64), ("kc_sH", i64), ("kc_sD", i64),
+                ("kscale", vp), ("kmn", vp), ("ks_sB", i64), ("ks_sH", i64), ("ks_sD", i64),
+                ("vcode", vp), ("vc_sB", i64), ("vc_sH", i64), ("vc_sT", i64),
+                ("vscale", vp), ("vmn", vp), ("vs_sB", i64), ("vs_sH", i64), ("vs_sT", i64),
+                ("kfull", vp), ("kf_sB", i64), ("kf_sH", i64), ("kf_sT", i64),
+                ("vfull", vp), ("vf_sB", i64), ("vf_sH", i64), ("vf_sT", i64)]
 
 
 class AttnPlan(C.Structure):
@@ -108,6 +123,10 @@ def lib():
             fn.argtypes = [C.POINTER(AppendFormArgs), vp]
         L.kvq_decode_attn_plan.restype = C.c_int
         L.kvq_decode_attn_plan.argtypes = [C.POINTER(AttnArgs), i32, C.POINTER(AttnPlan)]
+        L.kvq_peer_wait.restype = C.c_int
+        L.kvq_peer_wait.argtypes = [vp, C.c_uint32, C.c_uint32, vp, vp]
+        L.kvq_prefill.restype = C.c_int
+        L.kvq_prefill.argtypes = [C.POINTER(PrefillArgs), vp]
         L.kvq_decode_attn_workspace_init.restype = C.c_int
         L.kvq_decode_attn_workspace_init.argtypes = [vp, u64, i32, i32, vp]
         L.kvq_decode_attn_workspace_bytes.restype = u64
@@ -118,7 +137,7 @@ def lib():
 
 EXPORTS = ["kvq_version", "kvq_error_string", "kvq_last_cuda_error", "kvq_features_per_int",
            "kvq_quant_lastdim", "kvq_append_kv", "kvq_gemv", "kvq_decode_attn", "kvq_decode_attn_workspace_bytes",
-           "kvq_decode_attn_static", "kvq_decode_attn_plan", "kvq_decode_attn_workspace_init", "kvq_append_k", "kvq_append_v"]
+           "kvq_decode_attn_static", "kvq_decode_attn_plan", "kvq_decode_attn_workspace_init", "kvq_prefill", "kvq_peer_wait", "kvq_append_k", "kvq_append_v"]
 
 
 def check(rc):

@@ -147,6 +147,50 @@ class KVmixLayerCache:
         self.k_len, self.v_len = L - nk, L - nv
         self.kv_seq_len = L
 
+    def prefill_projected(self, k_proj, v_proj, cos=None, sin=None):
+        """Prefill straight from the projections (upstream :213-254 plus the rotary embedding before it).
+        k_proj, v_proj: the k_proj / v_proj outputs of the prompt, [B, L, Hkv*D] (or [B, L, Hkv, D]) fp16, keys NOT yet
+        rotated; cos, sin: the rotary tables [L, D] or [B, L, D] fp16 as HF's rotary embedding returns them (None: the
+        keys arrive rotated).  Rotation, the split into packed prefix and fp16 tail, both quantizers and the tail
+        copies run in three launches of the library; no rotated, transposed or sliced temporary is made."""
+        assert self.kv_seq_len == 0, "prefill needs an empty cache"
+        B, L = k_proj.shape[0], k_proj.shape[1]
+        k4, v4 = k_proj.reshape(B, L, self.Hkv, self.D), v_proj.reshape(B, L, self.Hkv, self.D)
+        if B != self.B or k4.dtype != torch.float16 or v4.dtype != torch.float16 or k4.stride(3) != 1 or v4.stride(3) != 1:
+            raise RuntimeError("prefill_projected takes fp16 projections [B, L, Hkv*D] of the cache's batch")
+        if L > self.max_tokens:
+            raise RuntimeError("prompt longer than the cache capacity")
+        nk = split_point(L, self.k_group, self.rk, self.window)
+        nv = split_point(L, self.v_group, self.rv, self.window)
+        if L - nk > self.k_cap or L - nv > self.v_cap:
+            raise RuntimeError("fp16 tail larger than the ring capacity (raise max_tail)")
+        a = _lib.PrefillArgs()
+        a.k, a.k_sB, a.k_sT, a.k_sH = k4.data_ptr(), k4.stride(0), k4.stride(1), k4.stride(2)
+        a.v, a.v_sB, a.v_sT, a.v_sH = v4.data_ptr(), v4.stride(0), v4.stride(1), v4.stride(2)
+        if cos is not None:
+            if cos.dtype != torch.float16 or sin.dtype != torch.float16 or cos.stride(-1) != 1 or sin.stride() != cos.stride():
+                raise RuntimeError("rotary tables must be fp16 with the same layout, contiguous along head_dim")
+            c3 = cos if cos.dim() == 3 else cos[None]
+            if c3.shape[-2] < L or c3.shape[-1] != self.D or c3.shape[0] not in (1, B):
+                raise RuntimeError("rotary tables must cover [L, head_dim]")
+            a.cos, a.sin = cos.data_ptr(), sin.data_ptr()
+            a.r_sB, a.r_sT = (c3.stride(0) if c3.shape[0] == B and B > 1 else 0), c3.stride(1)
+        a.B, a.Hkv, a.L, a.D, a.nk, a.nv = B, self.Hkv, L, self.D, nk, nv
+        a.k_bits, a.k_group, a.v_bits, a.v_group = self.k_bits, self.k_group, self.v_bits, self.v_group
+        kc, ks, vc, vs, kf, vf = self.kcode, self.kscale, self.vcode, self.vscale, self.kfull, self.vfull
+        a.kcode, a.kc_sB, a.kc_sH, a.kc_sD = kc.data_ptr(), kc.stride(0), kc.stride(1), kc.stride(2)
+        a.kscale, a.kmn, a.ks_sB, a.ks_sH, a.ks_sD = ks.data_ptr(), self.kmn.data_ptr(), ks.stride(0), ks.stride(1), ks.stride(2)
+        a.vcode, a.vc_sB, a.vc_sH, a.vc_sT = vc.data_ptr(), vc.stride(0), vc.stride(1), vc.stride(2)
+        a.vscale, a.vmn, a.vs_sB, a.vs_sH, a.vs_sT = vs.data_ptr(), self.vmn.data_ptr(), vs.stride(0), vs.stride(1), vs.stride(2)
+        a.kfull, a.kf_sB, a.kf_sH, a.kf_sT = kf.data_ptr(), kf.stride(0), kf.stride(1), kf.stride(2)
+        a.vfull, a.vf_sB, a.vf_sH, a.vf_sT = vf.data_ptr(), vf.stride(0), vf.stride(1), vf.stride(2)
+        _lib.check(self._lib.kvq_prefill(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        ops.LAUNCHES[0] += (nk > 0) + (nv > 0) + (nk < L or nv < L)
+        self.tkq, self.tvq = nk, nv
+        self.k_start = self.v_start = 0
+        self.k_len, self.v_len = L - nk, L - nv
+        self.kv_seq_len = L
+
     def append(self, k_new, v_new):
         """k_new, v_new: [B,Hkv,1,D] fp16.  Upstream decode branch, :111-167."""
         if self.kv_seq_len + 1 > self.max_tokens:

@@ -14,7 +14,7 @@ int record_cuda_error(cudaError_t e) {
 }
 }  // namespace kvq
 
-extern "C" int kvq_version(void) { return 103; }   // 103: fused decode step (kvq_attn_args.k_new ...), kvq_attn_plan, workspace_init, flags
+extern "C" int kvq_version(void) { return 104; }   // 104: fused decode step, head-sharded exchange, kvq_prefill, kvq_attn_plan, workspace_init
 
 extern "C" int kvq_features_per_int(int bits) { return (bits >= 1 && bits <= 4) ? kvq::fields_per_word(bits) : 0; }
 

@@ -42,3 +42,28 @@ extern "C" int kvq_append_kv(const kvq_append_args *a, kvq_stream_t stream) {
     append_kv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a);
     return check_launch();
 }
+
+
+// ---------------------------------------------------------------------------------------------
+// Bounded wait for the arrival counter of the head-sharded exchange (see kvq_peer_wait in the header).
+namespace kvq {
+__global__ void peer_wait_kernel(const uint32_t *counter, uint32_t expected, uint32_t max_polls, int32_t *status) {
+    uint32_t seen = 0;
+    for (uint32_t i = 0; i < max_polls; ++i) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+        if ((int32_t)(seen - expected) >= 0) return;
+        __nanosleep(1000);
+    }
+    status[0] = 1;                                             // gave up: the host reads this after the step
+    status[1] = (int32_t)seen;
+}
+}  // namespace kvq
+
+extern "C" int kvq_peer_wait(const uint32_t *counter, uint32_t expected, uint32_t max_polls, int32_t *status,
+                             kvq_stream_t stream) {
+    using namespace kvq;
+    if (!counter || !status) return KVQ_ERR_NULL;
+    if (max_polls == 0) return KVQ_ERR_SHAPE;
+    peer_wait_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(counter, expected, max_polls, status);
+    return check_launch();
+}

@@ -410,6 +410,12 @@ extern "C" int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream) {
 
     const AttnLaunch L = plan_launch(*a);
     if (L.ctas > 2147483647LL) return KVQ_ERR_UNSUPPORTED;
+    if (a->n_peers != 0) {                                     // head-sharded exchange (see the header)
+        if (a->n_peers < 0 || a->n_peers > KVQ_MAX_PEERS || a->peer_head0 < 0) return KVQ_ERR_SHAPE;
+        if (!L.use_mma) return KVQ_ERR_UNSUPPORTED;
+        for (int p = 0; p < a->n_peers; ++p)
+            if (!a->peer_out[p] || !a->peer_flag[p]) return KVQ_ERR_NULL;
+    }
     if (a->k_new || a->v_new) {                                // fused decode step (see the header)
         if (!a->k_new || !a->v_new) return KVQ_ERR_NULL;
         const int n_rep = a->nh / a->nh_kv;

@@ -687,11 +687,14 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, int n_scores
         }
         o[hs] = v;
     }
+    __half res[kQH];
     if (cnt == 1) {
         for (int hs = 0; hs < qhv; ++hs) {
             __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)(h_first + hs) * a.o_sH;
-            out[tid] = __float2half_rn(o[hs] / sm.misc[4 + hs]);
+            res[hs] = __float2half_rn(o[hs] / sm.misc[4 + hs]);
+            out[tid] = res[hs];
         }
+        peer_publish(a, b, h_first, qhv, res, tid);
         return;
     }
     float *part = parts + ((int64_t)(s - n_whole) * cnt + seg) * qhv * kPart;    // partials of the cut head groups only
@@ -719,9 +722,11 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, int n_scores
             acc = fmaf(__ldcg(bh + i * qhv * kPart + tid), w, acc);
         }
         __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)(h_first + hs) * a.o_sH;
-        out[tid] = __float2half_rn(acc / L);
+        res[hs] = __float2half_rn(acc / L);
+        out[tid] = res[hs];
     }
     if (tid == 0) counters[s] = 0u;
+    peer_publish(a, b, h_first, qhv, res, tid);
 }
 
 template <int KB, int VB>

@@ -749,7 +749,9 @@ __device__ __forceinline__ void attn_segment(const kvq_attn_args &a, int n_score
     }
     __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)h * a.o_sH;
     if (cnt == 1) {
-        out[tid] = __float2half_rn(o / l);
+        const __half r = __float2half_rn(o / l);
+        out[tid] = r;
+        peer_publish(a, b, h, 1, &r, tid);
         return;
     }
     constexpr int kPart = kHeadDim + 2;
@@ -775,8 +777,10 @@ __device__ __forceinline__ void attn_segment(const kvq_attn_args &a, int n_score
         L = fmaf(__ldcg(base + i * kPart + kHeadDim + 1), w, L);
         acc = fmaf(__ldcg(base + i * kPart + tid), w, acc);
     }
-    out[tid] = __float2half_rn(acc / L);
+    const __half r = __float2half_rn(acc / L);
+    out[tid] = r;
     if (tid == 0) counters[s] = 0u;                          // the head is done: its counter is ready for the next launch
+    peer_publish(a, b, h, 1, &r, tid);
 }
 
 // CTA = one segment (see attn_plan.cuh): a whole head, or one of the k pieces of a head that is cut.

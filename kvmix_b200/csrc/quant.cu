@@ -119,10 +119,19 @@ struct StridedCfg {
     static constexpr int WPAD = WPC + 1;
 };
 
-template <int BITS, int G>
+// Rotary embedding applied while loading (prefill of keys straight from the k_proj output): element (b, s, c) of the
+// cos / sin tables at b * r_sB + s * r_sS + c, fp16.  HF's rotate_half form (the one upstream's model files import):
+// out[c] = k[c] * cos[c] + rot[c] * sin[c] with rot = (-k[c + 64], k[c - 64]) for c < 64 / c >= 64, every product and
+// the sum rounded to fp16 as the framework's fp16 tensor arithmetic rounds them.
+struct RopeTables {
+    const __half *cos, *sin;
+    int64_t r_sB, r_sS;
+};
+
+template <int BITS, int G, bool ROPE>
 __global__ void __launch_bounds__(256, 3) quant_strided_kernel(const __half *__restrict__ x, int32_t *__restrict__ code,
                                                             __half *__restrict__ scale, __half *__restrict__ mn,
-                                                            QuantDims d) {
+                                                            QuantDims d, RopeTables rope) {
     using C = StridedCfg<BITS, G>;
     __shared__ int32_t s_code[128 * C::WPAD];
     __shared__ __half s_scale[128 * (C::GPC + 2)];
@@ -136,12 +145,28 @@ __global__ void __launch_bounds__(256, 3) quant_strided_kernel(const __half *__r
     const int groups_here = (int)min((int64_t)C::GPC, n_groups - g0);
     const __half *px = x + b * d.x_sB + h * d.x_sH + (a0 + 2 * pair);
     constexpr int QMAX = (1 << BITS) - 1;
+    // element pair (2 pair, 2 pair + 1) of token s of this (b, h) slab, rotated on the way in when ROPE
+    const int partner = (2 * pair < 64) ? 64 : -64;
+    const __half *pcos = ROPE ? rope.cos + b * rope.r_sB + 2 * pair : nullptr;
+    const __half *psin = ROPE ? rope.sin + b * rope.r_sB + 2 * pair : nullptr;
+    auto load = [&](int64_t s) -> __half2 {
+        const __half2 k = __ldg(reinterpret_cast<const __half2 *>(px + s * d.x_sS));
+        if constexpr (ROPE) {
+            __half2 r = __ldg(reinterpret_cast<const __half2 *>(px + s * d.x_sS + partner));
+            if (partner > 0) r = __hneg2(r);
+            const __half2 cs = __ldg(reinterpret_cast<const __half2 *>(pcos + s * rope.r_sS));
+            const __half2 sn = __ldg(reinterpret_cast<const __half2 *>(psin + s * rope.r_sS));
+            return __hadd2_rn(__hmul2_rn(k, cs), __hmul2_rn(r, sn));
+        } else {
+            return k;
+        }
+    };
 
     constexpr int CH = G > 32 ? 32 : G;                       // tokens held in registers at a time
     constexpr int NCH = G / CH;
     constexpr int WPCH = CH / C::FPI;                         // words per chunk (1 for the 11-token group)
     for (int g = slot; g < groups_here; g += 4) {
-        const __half *pg = px + (g0 + g) * G * d.x_sS;
+        const int64_t s0 = (g0 + g) * G;                      // first token of the group
         __half2 raw[CH];
         // min / max of the two channels in fp16x2 (exact: the data are fp16; NaN operands are skipped as by fminf)
         __half2 lo2 = __floats2half2_rn(65504.f, 65504.f), hi2 = __floats2half2_rn(-65504.f, -65504.f);
@@ -149,7 +174,7 @@ __global__ void __launch_bounds__(256, 3) quant_strided_kernel(const __half *__r
 #pragma unroll 1
         for (int c = 0; c < NCH; ++c) {
 #pragma unroll
-            for (int i = 0; i < CH; ++i) raw[i] = __ldg(reinterpret_cast<const __half2 *>(pg + (int64_t)(c * CH + i) * d.x_sS));
+            for (int i = 0; i < CH; ++i) raw[i] = load(s0 + c * CH + i);
             if (first) { lo2 = raw[0]; hi2 = raw[0]; first = false; }
 #pragma unroll
             for (int i = 0; i < CH; ++i) { lo2 = __hmin2(lo2, raw[i]); hi2 = __hmax2(hi2, raw[i]); }
@@ -161,7 +186,7 @@ __global__ void __launch_bounds__(256, 3) quant_strided_kernel(const __half *__r
         for (int c = 0; c < NCH; ++c) {
             if (NCH > 1) {                                    // long groups: second pass over the chunk (cache hit)
 #pragma unroll
-                for (int i = 0; i < CH; ++i) raw[i] = __ldg(reinterpret_cast<const __half2 *>(pg + (int64_t)(c * CH + i) * d.x_sS));
+                for (int i = 0; i < CH; ++i) raw[i] = load(s0 + c * CH + i);
             }
 #pragma unroll
             for (int w = 0; w < WPCH; ++w) {
@@ -252,7 +277,7 @@ __global__ void __launch_bounds__(128) quant_generic_kernel(const T *__restrict_
 
 // ---------------------------------------------------------------------------------------------
 template <int BITS, typename T>
-static int launch_bits(const kvq_quant_args *a, const QuantDims &d, cudaStream_t st) {
+static int launch_bits(const kvq_quant_args *a, const QuantDims &d, cudaStream_t st, const RopeTables *rope = nullptr) {
     constexpr int E = fields_per_word(BITS);
     const T *x = static_cast<const T *>(a->x);
     T *sc = static_cast<T *>(a->scale), *mn = static_cast<T *>(a->mn);
@@ -261,7 +286,7 @@ static int launch_bits(const kvq_quant_args *a, const QuantDims &d, cudaStream_t
     if (total_words == 0) return KVQ_OK;
 
     // groups along the contiguous axis
-    if (a->x_sS == 1 && G % E == 0) {
+    if (!rope && a->x_sS == 1 && G % E == 0) {
         bool vec_ok = sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && d.x_sB % 8 == 0 &&
                       d.x_sH % 8 == 0 && d.x_sA % 8 == 0;
         // 32 elements (64 B of fp16 in flight) per thread where the group and the row allow it: 4 / 2 words for 4 / 2 bits
@@ -292,7 +317,8 @@ static int launch_bits(const kvq_quant_args *a, const QuantDims &d, cudaStream_t
     {                                                                                              \
         using C = StridedCfg<BITS, GG>;                                                            \
         dim3 grid((unsigned)((ng + C::GPC - 1) / C::GPC), (unsigned)(d.A / 128), (unsigned)(d.B * d.H)); \
-        quant_strided_kernel<BITS, GG><<<grid, 256, 0, st>>>(xh, a->code, sh, mh, d);              \
+        if (rope) quant_strided_kernel<BITS, GG, true><<<grid, 256, 0, st>>>(xh, a->code, sh, mh, d, *rope);      \
+        else quant_strided_kernel<BITS, GG, false><<<grid, 256, 0, st>>>(xh, a->code, sh, mh, d, RopeTables{});   \
         return check_launch();                                                                     \
     }
             if constexpr (BITS == 3) {
@@ -305,14 +331,21 @@ static int launch_bits(const kvq_quant_args *a, const QuantDims &d, cudaStream_t
 #undef KVQ_LAUNCH_STRIDED
         }
     }
+    if (rope) return KVQ_ERR_UNSUPPORTED;                      // rotation on the way in needs the strided-key layout
     const int64_t blocks = (total_words + 127) / 128;
     quant_generic_kernel<BITS, T><<<(unsigned)blocks, 128, 0, st>>>(x, a->code, sc, mn, d);
     return check_launch();
 }
 
+static int quant_lastdim_impl(const kvq_quant_args *a, kvq_stream_t stream, const RopeTables *rope);
+
 }  // namespace kvq
 
 extern "C" int kvq_quant_lastdim(const kvq_quant_args *a, kvq_stream_t stream) {
+    return kvq::quant_lastdim_impl(a, stream, nullptr);
+}
+
+static int kvq::quant_lastdim_impl(const kvq_quant_args *a, kvq_stream_t stream, const RopeTables *rope) {
     using namespace kvq;
     if (!a) return KVQ_ERR_NULL;
     if (a->bits < 1 || a->bits > 4) return KVQ_ERR_BITS;
@@ -331,7 +364,7 @@ extern "C" int kvq_quant_lastdim(const kvq_quant_args *a, kvq_stream_t stream) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define KVQ_DISPATCH(BITS)                                                             \
     case BITS:                                                                         \
-        return a->x_is_f32 ? launch_bits<BITS, float>(a, d, st) : launch_bits<BITS, __half>(a, d, st);
+        return a->x_is_f32 ? launch_bits<BITS, float>(a, d, st, rope) : launch_bits<BITS, __half>(a, d, st, rope);
     switch (a->bits) {
         KVQ_DISPATCH(1)
         KVQ_DISPATCH(2)
@@ -419,4 +452,92 @@ extern "C" int kvq_append_v(const kvq_append_form_args *a, kvq_stream_t stream) 
                      a->mn ? static_cast<char *>(a->mn) + (size_t)(a->old_tokens * gpt) * es : nullptr,
                      a->H * Tt * gpt, Tt * gpt, gpt};
     return kvq_quant_lastdim(&q, stream);
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Prompt tails: tokens [nk, L) of the keys (rotated on the way when tables are given) and [nv, L) of the values go to
+// rows 0.. of the fp16 rings.  One thread per (b, h, token, 8-channel chunk j < 8) handles chunk j and chunk j + 8,
+// the rotation partners.
+namespace kvq {
+__global__ void __launch_bounds__(256) prefill_tails_kernel(kvq_prefill_args a) {
+    const int D = a.D, nkt = a.L - a.nk, nvt = a.L - a.nv;
+    const int64_t per_k = (int64_t)a.B * a.Hkv * nkt * 8, per_v = (int64_t)a.B * a.Hkv * nvt * 8;
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= per_k + per_v) return;
+    const bool is_v = i >= per_k;
+    if (is_v) i -= per_k;
+    const int j = (int)(i & 7);
+    const int n = is_v ? nvt : nkt;
+    const int64_t r = (i >> 3) % n, bh = (i >> 3) / n;
+    const int b = (int)(bh / a.Hkv), h = (int)(bh % a.Hkv);
+    if (is_v) {
+        const __half *src = static_cast<const __half *>(a.v) + b * a.v_sB + (a.nv + r) * a.v_sT + h * a.v_sH;
+        __half *dst = static_cast<__half *>(a.vfull) + b * a.vf_sB + h * a.vf_sH + r * a.vf_sT;
+        reinterpret_cast<uint4 *>(dst)[j] = __ldg(reinterpret_cast<const uint4 *>(src) + j);
+        reinterpret_cast<uint4 *>(dst)[j + 8] = __ldg(reinterpret_cast<const uint4 *>(src) + j + 8);
+        return;
+    }
+    const int64_t t = a.nk + r;
+    const __half *src = static_cast<const __half *>(a.k) + b * a.k_sB + t * a.k_sT + h * a.k_sH;
+    __half *dst = static_cast<__half *>(a.kfull) + b * a.kf_sB + h * a.kf_sH + r * a.kf_sT;
+    uint4 lo = __ldg(reinterpret_cast<const uint4 *>(src) + j), hi = __ldg(reinterpret_cast<const uint4 *>(src) + j + 8);
+    if (a.cos) {
+        const __half *pc = static_cast<const __half *>(a.cos) + b * a.r_sB + t * a.r_sT;
+        const __half *ps = static_cast<const __half *>(a.sin) + b * a.r_sB + t * a.r_sT;
+        const uint4 cl = __ldg(reinterpret_cast<const uint4 *>(pc) + j), ch = __ldg(reinterpret_cast<const uint4 *>(pc) + j + 8);
+        const uint4 sl = __ldg(reinterpret_cast<const uint4 *>(ps) + j), sh = __ldg(reinterpret_cast<const uint4 *>(ps) + j + 8);
+        uint4 ol, oh;
+        const __half2 *kl = reinterpret_cast<const __half2 *>(&lo), *kh = reinterpret_cast<const __half2 *>(&hi);
+        const __half2 *c0 = reinterpret_cast<const __half2 *>(&cl), *c1 = reinterpret_cast<const __half2 *>(&ch);
+        const __half2 *s0 = reinterpret_cast<const __half2 *>(&sl), *s1 = reinterpret_cast<const __half2 *>(&sh);
+        __half2 *pl = reinterpret_cast<__half2 *>(&ol), *ph = reinterpret_cast<__half2 *>(&oh);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            pl[q] = __hadd2_rn(__hmul2_rn(kl[q], c0[q]), __hmul2_rn(__hneg2(kh[q]), s0[q]));
+            ph[q] = __hadd2_rn(__hmul2_rn(kh[q], c1[q]), __hmul2_rn(kl[q], s1[q]));
+        }
+        lo = ol;
+        hi = oh;
+    }
+    reinterpret_cast<uint4 *>(dst)[j] = lo;
+    reinterpret_cast<uint4 *>(dst)[j + 8] = hi;
+    (void)D;
+}
+}  // namespace kvq
+
+extern "C" int kvq_prefill(const kvq_prefill_args *a, kvq_stream_t stream) {
+    using namespace kvq;
+    if (!a) return KVQ_ERR_NULL;
+    if (a->D != kHeadDim) return KVQ_ERR_UNSUPPORTED;
+    if (a->B <= 0 || a->Hkv <= 0 || a->L <= 0) return KVQ_OK;
+    if (a->nk < 0 || a->nv < 0 || a->nk > a->L || a->nv > a->L) return KVQ_ERR_TOKENS;
+    if (!a->k || !a->v) return KVQ_ERR_NULL;
+    if ((a->cos == nullptr) != (a->sin == nullptr)) return KVQ_ERR_NULL;
+    if (a->k_bits < 1 || a->k_bits > 4 || a->v_bits < 1 || a->v_bits > 4) return KVQ_ERR_BITS;
+    auto al16 = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    if (!al16(a->k) || !al16(a->v) || a->k_sB % 8 || a->k_sT % 8 || a->k_sH % 8 || a->v_sB % 8 || a->v_sT % 8 || a->v_sH % 8)
+        return KVQ_ERR_ALIGN;
+    if (a->cos && (!al16(a->cos) || !al16(a->sin) || a->r_sB % 8 || a->r_sT % 8)) return KVQ_ERR_ALIGN;
+    if (a->nk < a->L && (!a->kfull || !al16(a->kfull) || a->kf_sB % 8 || a->kf_sH % 8 || a->kf_sT % 8)) return KVQ_ERR_ALIGN;
+    if (a->nv < a->L && (!a->vfull || !al16(a->vfull) || a->vf_sB % 8 || a->vf_sH % 8 || a->vf_sT % 8)) return KVQ_ERR_ALIGN;
+    if (a->nk > 0) {                                           // keys: groups over tokens, channels contiguous, read in place
+        kvq_quant_args q{a->k, 0, a->B, a->Hkv, a->D, a->nk, a->k_sB, a->k_sH, 1, a->k_sT, a->k_group, a->k_bits, 0,
+                         a->kcode, a->kc_sB, a->kc_sH, a->kc_sD, a->kscale, a->kmn, a->ks_sB, a->ks_sH, a->ks_sD};
+        RopeTables rope{static_cast<const __half *>(a->cos), static_cast<const __half *>(a->sin), a->r_sB, a->r_sT};
+        const int rc = quant_lastdim_impl(&q, stream, a->cos ? &rope : nullptr);
+        if (rc) return rc;
+    }
+    if (a->nv > 0) {                                           // values: groups over channels
+        kvq_quant_args q{a->v, 0, a->B, a->Hkv, a->nv, a->D, a->v_sB, a->v_sH, a->v_sT, 1, a->v_group, a->v_bits, 0,
+                         a->vcode, a->vc_sB, a->vc_sH, a->vc_sT, a->vscale, a->vmn, a->vs_sB, a->vs_sH, a->vs_sT};
+        const int rc = kvq_quant_lastdim(&q, stream);
+        if (rc) return rc;
+    }
+    const int64_t n = (int64_t)a->B * a->Hkv * ((int64_t)(a->L - a->nk) + (a->L - a->nv)) * 8;
+    if (n > 0) {
+        prefill_tails_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a);
+        return check_launch();
+    }
+    return KVQ_OK;
 }

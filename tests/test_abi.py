@@ -46,7 +46,7 @@ def test_struct_sizes_match_header():
     src = r'''
 #include <stdio.h>
 #include "kvmix_b200.h"
-int main(void){ printf("%zu %zu %zu %zu %zu\n", sizeof(kvq_quant_args), sizeof(kvq_gemv_args), sizeof(kvq_attn_args), sizeof(kvq_append_args), sizeof(kvq_append_form_args)); return 0; }
+int main(void){ printf("%zu %zu %zu %zu %zu %zu %zu\n", sizeof(kvq_quant_args), sizeof(kvq_gemv_args), sizeof(kvq_attn_args), sizeof(kvq_append_args), sizeof(kvq_append_form_args), sizeof(kvq_prefill_args), sizeof(kvq_attn_plan)); return 0; }
 '''
     with tempfile.TemporaryDirectory() as d:
         c = os.path.join(d, "s.c")
@@ -55,7 +55,8 @@ int main(void){ printf("%zu %zu %zu %zu %zu\n", sizeof(kvq_quant_args), sizeof(k
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
         sizes = [int(x) for x in subprocess.check_output([exe]).split()]
     assert sizes == [ctypes.sizeof(_lib.QuantArgs), ctypes.sizeof(_lib.GemvArgs), ctypes.sizeof(_lib.AttnArgs),
-                     ctypes.sizeof(_lib.AppendArgs), ctypes.sizeof(_lib.AppendFormArgs)]
+                     ctypes.sizeof(_lib.AppendArgs), ctypes.sizeof(_lib.AppendFormArgs), ctypes.sizeof(_lib.PrefillArgs),
+                     ctypes.sizeof(_lib.AttnPlan)]
 
 
 def test_argument_errors_need_no_gpu():
