@@ -362,6 +362,9 @@ def main():
     ap.add_argument("--context", type=int, default=None, help="override the context length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-upstream-gpu", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="config 5 on several GPUs: attention outputs exchanged by peer stores from the attention kernel "
+                         "(default; falls back to NCCL when symmetric memory is unavailable) or by an NCCL all-gather per layer")
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
                     help="2: Llama-2-7B b64 ctx4k (the headline, batch-sharded); 3: Mistral-7B GQA b8 ctx32k (batch-sharded); "
                          "4: quantize-on-append sweep (GB/s, batch-sharded); "
@@ -421,7 +424,16 @@ def main():
     hk = [t.cpu().pin_memory() for t in dk]
     hv = [t.cpu().pin_memory() for t in dv]
     hout = [torch.empty((B, nh, 1, D), dtype=torch.float16).pin_memory() for _ in range(L)]
-    gather = sharding.HeadGather(B, nh, D, torch.float16, dev) if head_sharded else None
+    gather = peer = None
+    if head_sharded:
+        if args.exchange == "peer" and sharding.PeerGather.available():
+            try:
+                peer = sharding.PeerGather(B, nh, D, dev)
+            except Exception as e:                              # symmetric memory not usable here: the NCCL exchange still is
+                if rank == 0:
+                    print(f"peer exchange unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr)
+        if peer is None:
+            gather = sharding.HeadGather(B, nh, D, torch.float16, dev)
 
     attn_events = []
 
@@ -431,12 +443,14 @@ def main():
             if record:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                c.decode_step(dq[l], dk[l], dv[l], out=dout[l])
+                c.decode_step(dq[l], dk[l], dv[l], out=dout[l], peers=peer)
                 e1.record()
                 attn_events.append((e0, e1, c.packed_bytes() + 2 * B * nh * D * 2, (c.k_bits, c.v_bits)))
             else:
-                c.decode_step(dq[l], dk[l], dv[l], out=dout[l])
-            if head_sharded:                                    # the one exchange step of the path (NCCL over NVLink)
+                c.decode_step(dq[l], dk[l], dv[l], out=dout[l], peers=peer)
+            if peer is not None:                                # the one exchange step of the path: peer stores from the
+                peer.wait()                                     # attention kernel + a bounded wait for all ranks' rows
+            elif head_sharded:                                  # or one NCCL all-gather per layer
                 gather(dout[l])
 
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
@@ -467,8 +481,10 @@ def main():
                 if prefetch and l + 1 < L:
                     copy_in(l + 1)
                 cur.wait_event(ev_in[l])
-                caches[l].decode_step(dq[l], dk[l], dv[l], out=dout[l])
-                if head_sharded:
+                caches[l].decode_step(dq[l], dk[l], dv[l], out=dout[l], peers=peer)
+                if peer is not None:
+                    peer.wait()
+                elif head_sharded:
                     gather(dout[l])
                 ev_done[l].record(cur)
                 with torch.cuda.stream(s_out):
@@ -536,6 +552,8 @@ def main():
     else:
         attn_ms_all, attn_bytes_all = attn_ms, float(attn_bytes)
 
+    if peer is not None:
+        peer.check()                                            # a wait that gave up raises here
     if rank == 0:
         peak, peak_src = measured_peak_gbs()
         achieved = attn_bytes_all / (attn_ms_all * 1e-3) / 1e9
@@ -557,7 +575,9 @@ def main():
                                   " (3-bit keys use group 11), seeded",
                        "l2_policy": "inputs larger than L2: every step streams the whole cache "
                                     f"({attn_bytes_all / max(1, n_attn) * L / 1e9:.1f} GB per step per GPU)",
-                       "parallelism": (f"kv-head-sharded x{world}, per-layer NCCL all-gather of the attention output"
+                       "parallelism": ((f"kv-head-sharded x{world}, attention outputs exchanged by peer stores from the attention "
+                                        f"kernel + bounded device-side wait (NVLink, no collective launch)" if peer is not None else
+                                        f"kv-head-sharded x{world}, per-layer NCCL all-gather of the attention output")
                                        if head_sharded else f"batch-sharded x{world}, no data-path collective")},
             "roofline": {"bound": "hbm", "kernel": "decode_attn_gqa_kernel" if cfg.n_heads != cfg.n_kv_heads else "decode_attn_mma_kernel",
                          "achieved": achieved, "peak": peak,

@@ -221,7 +221,7 @@ class KVmixLayerCache:
             ws = self._ws[(nh, stream)] = torch.zeros(need, dtype=torch.uint8, device=device)
         return ws
 
-    def attend(self, q, out=None, round_scores=True, attention_mask=None):
+    def attend(self, q, out=None, round_scores=True, attention_mask=None, peers=None):
         """q: [B,nh,1,D] fp16 -> [B,nh,1,D] fp16 over everything cached (upstream :170-211).  attention_mask:
         optional additive mask over the kv_seq_len cached positions ([B,1,1,T], [B,nh,1,T] or [B,T]; upstream
         :188-193), e.g. the left-padding mask of a ragged batch."""
@@ -244,23 +244,27 @@ class KVmixLayerCache:
         a.kf_start, a.vf_start = self.k_start, self.v_start
         a.workspace, a.workspace_bytes, a.flags = ws.data_ptr(), ws.numel(), _lib.ATTN_WORKSPACE_READY
         a.mask, a.mask_sB, a.mask_sH, a.mask_is_f32 = ops.mask_fields(attention_mask, B, nh, a.T)
-        _lib.check(self._lib.kvq_decode_attn(C.byref(a), C.c_void_p(stream)))
+        if peers is not None:
+            peers.fill(a)
+        rc = self._lib.kvq_decode_attn(C.byref(a), C.c_void_p(stream))
+        a.n_peers = 0
+        _lib.check(rc)
         ops.LAUNCHES[0] += 1
         return out
 
-    def decode_step(self, q, k_new, v_new, out=None, attention_mask=None, round_scores=True):
+    def decode_step(self, q, k_new, v_new, out=None, attention_mask=None, round_scores=True, peers=None):
         """Upstream's decode branch for one new token (:105-211): cache update, then attention over everything cached.
         One launch when the library can fuse the update into the attention kernel (one CTA per kv head and segment:
         MHA, or grouped queries with 2 or 4 query heads per kv head, on the tensor-core kernels); otherwise the ring
         append, the group quantizers and the attention are launched one after the other (``append`` + ``attend``)."""
         if self._fused is not False:
-            res = self._decode_step_fused(q, k_new, v_new, out, attention_mask, round_scores)
+            res = self._decode_step_fused(q, k_new, v_new, out, attention_mask, round_scores, peers)
             if res is not None:
                 return res
         self.append(k_new, v_new)
-        return self.attend(q, out=out, attention_mask=attention_mask, round_scores=round_scores)
+        return self.attend(q, out=out, attention_mask=attention_mask, round_scores=round_scores, peers=peers)
 
-    def _decode_step_fused(self, q, k_new, v_new, out, attention_mask, round_scores):
+    def _decode_step_fused(self, q, k_new, v_new, out, attention_mask, round_scores, peers=None):
         B, nh, M, D = q.shape
         if M != 1 or B != self.B or D != self.D or not q.is_cuda:
             raise RuntimeError("decode_step takes q [B, nh, 1, D] on the cache's device")
@@ -292,9 +296,11 @@ class KVmixLayerCache:
         a.k_new, a.kn_sB, a.kn_sH = k_new.data_ptr(), k_new.stride(0), k_new.stride(1)
         a.v_new, a.vn_sB, a.vn_sH = v_new.data_ptr(), v_new.stride(0), v_new.stride(1)
         a.k_quant, a.v_quant, a.k_quant_slot, a.v_quant_slot = nk, nv, self.k_start, self.v_start
+        if peers is not None:
+            peers.fill(a)
         rc = self._lib.kvq_decode_attn(C.byref(a), C.c_void_p(stream))
         a.k_new = a.v_new = None
-        a.k_quant = a.v_quant = 0
+        a.k_quant = a.v_quant = a.n_peers = 0
         if rc == -11:                                           # this geometry is not served fused: remember and fall back
             self._fused = False
             return None

@@ -75,6 +75,85 @@ class HeadGather:
         return self.out
 
 
+class PeerGather:
+    """The same exchange without a collective launch: every rank's attention kernel stores the rows it finishes
+    straight into all ranks' gather buffers (plain peer stores over NVLink, ``kvq_attn_args.peer_out``) and raises their
+    arrival counters; the consumer waits on its own counter with a bounded device-side poll (``kvq_peer_wait``).
+
+    ``depth`` gather buffers are used round-robin, one per layer: a rank that is ``depth`` layers ahead has already
+    seen every rank arrive ``depth - 1`` layers back, so nobody still reads the buffer it is about to overwrite.
+    Buffers and counters live in symmetric memory (``torch.distributed._symmetric_memory``); ``available()`` says
+    whether this process can use it.  ``peers`` may be given instead for tests: a list of (buffer, counters) tensors,
+    one pair per emulated rank, all on this GPU."""
+
+    MAX_POLLS = 2_000_000          # ~2 s of polling before a wait gives up and reports it
+
+    def __init__(self, batch, nh_local, head_dim, device, group=None, depth=2, peers=None, rank=None):
+        import ctypes as C
+        from . import _lib
+        self._C, self._lib = C, _lib.lib()
+        self.B, self.nhl, self.D, self.depth = batch, nh_local, head_dim, depth
+        if peers is None:
+            import torch.distributed._symmetric_memory as symm
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+            nh = self.world * nh_local
+            self.buf = symm.empty((depth, batch, nh, 1, head_dim), dtype=torch.float16, device=device)
+            self.cnt = symm.empty((depth * 32,), dtype=torch.int32, device=device)
+            self.buf.zero_()
+            self.cnt.zero_()
+            g = group if group is not None else dist.group.WORLD
+            hb, hc = symm.rendezvous(self.buf, g), symm.rendezvous(self.cnt, g)
+            self.buf_ptrs, self.cnt_ptrs = list(hb.buffer_ptrs), list(hc.buffer_ptrs)
+            torch.cuda.synchronize()
+            dist.barrier(group)
+        else:
+            self.world, self.rank = len(peers), rank or 0
+            self.buf, self.cnt = peers[self.rank]
+            self.buf_ptrs = [b.data_ptr() for b, _ in peers]
+            self.cnt_ptrs = [c.data_ptr() for _, c in peers]
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        self.status = torch.zeros(2, dtype=torch.int32, device=device)
+        self.uses = [0] * depth
+        self.layer = 0
+        self._slot_bytes = batch * self.world * nh_local * head_dim * 2
+
+    @staticmethod
+    def available():
+        try:
+            import torch.distributed._symmetric_memory as symm  # noqa: F401
+            return dist.is_initialized() and dist.get_backend() == "nccl"
+        except Exception:
+            return False
+
+    def fill(self, a):
+        """Point the exchange fields of a kvq_attn_args block at the next layer's gather buffer."""
+        slot = self.layer % self.depth
+        a.n_peers, a.peer_head0 = self.world, self.rank * self.nhl
+        for p in range(self.world):
+            a.peer_out[p] = self.buf_ptrs[p] + slot * self._slot_bytes
+            a.peer_flag[p] = self.cnt_ptrs[p] + slot * 128
+        a.peer_sB, a.peer_sH = self.world * self.nhl * self.D, self.D
+
+    def wait(self):
+        """Enqueue the bounded wait for the layer just launched; returns the gathered [B, nh, 1, D] view."""
+        slot = self.layer % self.depth
+        self.uses[slot] += 1
+        expected = (self.uses[slot] * self.B * self.world * self.nhl) & 0xFFFFFFFF
+        from . import _lib
+        _lib.check(self._lib.kvq_peer_wait(self._C.c_void_p(self.cnt.data_ptr() + slot * 128), expected, self.MAX_POLLS,
+                                           self._C.c_void_p(self.status.data_ptr()),
+                                           self._C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        self.layer += 1
+        return self.buf[slot]
+
+    def check(self):
+        """Host-side check after a step (synchronises): raises if a wait gave up."""
+        st = self.status.tolist()
+        if st[0]:
+            raise RuntimeError(f"head-sharded exchange: a rank's attention output did not arrive (counter at {st[1] & 0xFFFFFFFF})")
+
+
 def max_over_ranks(value, device, group=None):
     """The slowest rank's time: what a multi-GPU step costs."""
     t = torch.tensor([float(value)], device=device, dtype=torch.float64)
