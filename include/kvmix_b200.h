@@ -359,8 +359,10 @@ int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream);
 /*
  * How kvq_decode_attn would spread the call described by `a` (shapes, bit widths and group sizes are read; no pointer
  * is dereferenced) over CTAs.  No upstream counterpart: upstream's GEMV never splits a row.
- * The token axis of a head is cut into units of `unit` tokens.  Tensor-core kernels (tensor_core != 0; aligned caches,
- * see kvq_decode_attn): kernel 1 gives every query head its own CTAs, kernel 2 lets the heads_per_cta query heads that
+ * tensor_core > 0 asks for the tensor-core kernels' plan, 0 for the generic kernel's, < 0 for whichever
+ * kvq_decode_attn would run for `a` (then pointers and strides are inspected for alignment too).
+ * The token axis of a head is cut into units of `unit` tokens.  Tensor-core kernels (aligned caches, see
+ * kvq_decode_attn): kernel 1 gives every query head its own CTAs, kernel 2 lets the heads_per_cta query heads that
  * share a kv head share CTAs (chosen when nh / nh_kv is 2 or a multiple of 4 and the group sizes allow it).  The
  * first n_whole heads take one CTA each -- a multiple of the GPU's resident-CTA slots, so they fill whole waves -- and
  * each of the remaining n_cut heads is cut into `segments` pieces of segment_units units, launched after them, so

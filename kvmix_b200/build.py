@@ -21,11 +21,8 @@ def sources():
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
-PHASE_MARK = os.path.join(HERE, "lib", ".phase_timing")      # present while the built library carries the phase clock
-
-
 def _stale():
-    if not os.path.exists(LIB) or os.path.exists(PHASE_MARK):
+    if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
     deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + \
@@ -33,9 +30,7 @@ def _stale():
     return any(os.path.getmtime(p) > t for p in deps)
 
 
-def build(force=False, verbose=False, phase_timing=False):
-    """phase_timing adds the kernels' optional phase clock (-DKVQ_PHASE_TIMING, see `microbench phases`)."""
-    force = force or phase_timing
+def build(force=False, verbose=False):
     if not force and not _stale():
         return LIB
     os.makedirs(os.path.dirname(LIB), exist_ok=True)
@@ -46,8 +41,7 @@ def build(force=False, verbose=False, phase_timing=False):
     for src in sources():
         obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
-        cmd = (["nvcc", "-c", src, "-o", obj] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) +
-               (["-DKVQ_PHASE_TIMING"] if phase_timing else []))
+        cmd = ["nvcc", "-c", src, "-o", obj] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else [])
         procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for cmd, p in procs:
         out, _ = p.communicate()
@@ -57,12 +51,8 @@ def build(force=False, verbose=False, phase_timing=False):
         if p.returncode:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
     subprocess.check_call(["nvcc", "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"])
-    if phase_timing:
-        open(PHASE_MARK, "w").close()
-    elif os.path.exists(PHASE_MARK):
-        os.remove(PHASE_MARK)
     return LIB
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, phase_timing="--phase-timing" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -370,6 +370,9 @@ class KVmixLayerCache:
         if self.v_len:
             self.vfull[:, :, :self.v_len].copy_(vfull)
         self.kv_seq_len = int(seen)
+        if self.tkq + self.k_len != self.kv_seq_len or self.tvq + self.v_len != self.kv_seq_len:
+            self.reset()
+            raise RuntimeError("inconsistent token counts")
 
     def packed_bytes(self):
         """Bytes one attend() must read: codes + scale/zero + fp16 tails (the roofline numerator)."""

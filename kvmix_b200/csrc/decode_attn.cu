@@ -354,6 +354,7 @@ extern "C" int kvq_decode_attn_plan(const kvq_attn_args *a, int32_t tensor_core,
     if (a->B <= 0 || a->nh <= 0 || a->T <= 0) return KVQ_ERR_SHAPE;
     if (a->nh_kv <= 0 || a->nh % a->nh_kv != 0) return KVQ_ERR_HEADS;
     const int64_t heads = (int64_t)a->B * a->nh;
+    if (tensor_core < 0) tensor_core = mma_path_eligible(*a) ? 1 : 0;      // what kvq_decode_attn itself would pick
     if (tensor_core) {
         const int qhv = gqa_heads_per_cta(*a);
         const AttnPlan p = qhv ? plan_attn_gqa(a->T, a->k_bits, heads / qhv) : plan_attn_mma(a->T, a->k_bits, heads);

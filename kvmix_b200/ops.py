@@ -139,6 +139,8 @@ def quantized_gemm(group_size, fA, qB, scales, zeros, bits, out=None):
     if zeros.stride() != scales.stride() or zeros.stride(3) != 1:
         zeros = zeros.contiguous()
         scales = scales.contiguous()
+    if qB.shape[0] != B or qB.shape[2] != K or tuple(scales.shape[:3]) != (B, nh_kv, K) or zeros.shape != scales.shape:
+        check(-7)
     n_words, n_groups = qB.shape[3], zeros.shape[3]
     N = n_groups * group_size
     if out is None:
@@ -289,6 +291,19 @@ def decode_attention(q, kcode, kscale, kmn, kfull, vcode, vscale, vmn, vfull, k_
     Hkv = (kfull if kfull is not None else kcode).shape[1]
     if q.stride(3) != 1:
         q = q.contiguous()
+
+    def _rows(t):                                # packed tensors are indexed with unit stride along their last dim
+        return t if t is None or t.stride(3) == 1 else t.contiguous()
+
+    kcode, vcode, kfull, vfull = _rows(kcode), _rows(vcode), _rows(kfull), _rows(vfull)
+    if kscale is not None and (kscale.stride(3) != 1 or kmn.stride() != kscale.stride() or kmn.shape != kscale.shape):
+        kscale, kmn = kscale.contiguous(), kmn.contiguous()      # one set of strides serves scale and minimum
+    if vscale is not None and (vscale.stride(3) != 1 or vmn.stride() != vscale.stride() or vmn.shape != vscale.shape):
+        vscale, vmn = vscale.contiguous(), vmn.contiguous()
+    if kcode is not None and (kcode.shape[3] * fk < Tkq or kscale.shape[3] * k_group < Tkq):
+        check(-7)
+    if vcode is not None and (vcode.shape[2] < Tvq or vscale.shape[2] < Tvq):
+        check(-7)
     if out is None:
         out = torch.empty((B, nh, 1, D), dtype=torch.float16, device=q.device)
     if workspace is None:

@@ -11,10 +11,12 @@ variants are produced, both only into ``oracle/_ref/``:
   rounding, which is what the CPU restatement in this folder states bit-exactly.
 
 The modules have no CPU path, so they can only be *executed* on a machine with a GPU; there
-they are used by ``tests/golden/make_golden.py`` to pin the CPU restatement and by
-``bench.py`` as an extra, clearly labelled data point.  Nothing in the product imports them.
+they are used by ``tests/golden/make_golden.py`` and ``tests/golden/make_attn_golden.py`` to pin the CPU
+restatement and by ``bench.py``'s ``upstream_gpu`` leg (through ``oracle/upstream_torch.py``) as the clearly
+labelled "kernel to beat on the same GPU".  Nothing in the product imports them.
 
-Usage:  python oracle/build_ref.py [--ref /path/to/reference] [--variant fast|ieee|both]
+Usage:  python oracle/build_ref.py --ref /path/to/upstream/tree [--variant fast|ieee|both]
+        (or the tree's path in the environment variable KVMIX_REFERENCE)
 """
 import argparse
 import os
@@ -77,9 +79,12 @@ def build(ref, variant):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("KVMIX_REFERENCE", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get("KVMIX_REFERENCE"),
+                    help="root of the upstream KVmix tree (default: $KVMIX_REFERENCE)")
     ap.add_argument("--variant", default="both", choices=["fast", "ieee", "both"])
     a = ap.parse_args()
+    if not a.ref:
+        ap.error("give the upstream tree with --ref or KVMIX_REFERENCE")
     if not os.path.isdir(os.path.join(a.ref, "quant_cuda", "csrc")):
         print("reference tree not present; nothing to build")
         return 0

@@ -118,7 +118,7 @@ def test_split_merge_long_context_is_deterministic(cuda):
 
 @pytest.mark.parametrize("policy", ["window", "ratio"])
 @pytest.mark.parametrize("kb,vb,G", [(4, 2, 32), (3, 2, 32), (2, 1, 64)])
-@pytest.mark.parametrize("nh", [2, 4])      # 2 = one query head per kv head (tensor-core kernel), 4 = grouped queries
+@pytest.mark.parametrize("nh", [2, 4])      # 2 = one query head per kv head, 4 = two query heads per kv head (grouped kernel where the group sizes allow)
 def test_cache_decode_loop_matches_glue(cuda, policy, kb, vb, G, nh):
     """Prefill + 80 decode steps: the preallocated ring cache and upstream's cat-based protocol hold the
     same tokens in the same form at every step, and attention matches."""

@@ -32,8 +32,9 @@ def _args(cache, q, out, workspace):
                     0 if workspace is None else workspace.data_ptr(), 0 if workspace is None else workspace.numel())
 
 
-@pytest.mark.parametrize("nh,hkv,kb,vb,G", [(4, 4, 2, 2, 32), (8, 2, 4, 2, 64)])   # tensor-core path / generic path
-def test_static_scratch_matches_workspace_entry_point_twice(cuda, nh, hkv, kb, vb, G):
+# tensor-core kernel / grouped-query tensor-core kernel / generic CUDA-core kernel (groups of 16 are not a tensor-core layout)
+@pytest.mark.parametrize("nh,hkv,kb,vb,G,kernel", [(4, 4, 2, 2, 32, 1), (8, 2, 4, 2, 64, 2), (4, 2, 2, 2, 16, 0)])
+def test_static_scratch_matches_workspace_entry_point_twice(cuda, nh, hkv, kb, vb, G, kernel):
     import kvmix_b200 as kv
     from kvmix_b200 import _lib, configs
     L = _lib.lib()
@@ -46,6 +47,11 @@ def test_static_scratch_matches_workspace_entry_point_twice(cuda, nh, hkv, kb, v
     ws = torch.empty(need, dtype=torch.uint8, device=cuda)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     g = torch.Generator(device=cuda).manual_seed(1)
+    plan = _lib.AttnPlan()                                     # the kernel this case is meant to exercise, cut into several pieces
+    probe = _args(cache, torch.zeros((B, nh, 1, 128), device=cuda, dtype=torch.float16),
+                  torch.zeros((B, nh, 1, 128), device=cuda, dtype=torch.float16), ws)
+    assert L.kvq_decode_attn_plan(C.byref(probe), -1, C.byref(plan)) == 0
+    assert plan.kernel == kernel and plan.segments > 1
     for call in range(2):                             # two calls in a row: the second sees the first one's leftovers
         q = torch.randn((B, nh, 1, 128), generator=g, device=cuda, dtype=torch.float16)
         want = torch.zeros_like(q)
