@@ -34,7 +34,7 @@ DTYPE = "f16 data, f32 accumulate, u32 packed codes"
 
 # dram__bytes_read + dram__bytes_write over algorithmic bytes of one fused-attention launch, from the ncu captures
 # summarised in profiles/decode_attn_mma_kernel_B32_ctx4096.md (one CTA per head there, so the ratio carries over).
-NCU_TRAFFIC_RATIO = {(4, 4): 1.054, (3, 2): 1.047, (2, 2): 1.051}
+NCU_TRAFFIC_RATIO = {(4, 4): 1.056, (3, 2): 1.049, (2, 2): 1.051}
 
 
 def measured_peak_gbs():
