@@ -304,6 +304,10 @@ typedef struct {
     int64_t kn_sB, kn_sH, vn_sB, vn_sH;
     int32_t k_quant, v_quant;      /* tokens to quantize in this launch: 0, or exactly k_group / v_group */
     int32_t k_quant_slot, v_quant_slot;   /* ring row of the first of them */
+    /* Optional device-resident cache state (NULL: none); see "device-resident state" below. */
+    int32_t *state;
+    int32_t window;                /* fp16 tokens kept (>= 0), or < 0: keep int(ratio * current fp16 length) */
+    double k_ratio, v_ratio;
     /* Optional exchange fused into the launch (n_peers == 0: none); see "head-sharded exchange" below. */
     int32_t n_peers, peer_head0;
     void *peer_out[KVQ_MAX_PEERS];         /* [B, nh_total, D] fp16 gather buffer of every rank, strides peer_sB, peer_sH */
@@ -325,6 +329,19 @@ typedef struct {
  * Served by the tensor-core kernels when exactly one CTA reads a kv head's tokens: nh == nh_kv, or grouped queries
  * with nh / nh_kv in {2, 4} and group sizes the grouped kernel takes; otherwise KVQ_ERR_UNSUPPORTED is returned before
  * anything is launched and the caller runs kvq_append_kv / kvq_quant_lastdim / kvq_decode_attn separately.
+ */
+
+/*
+ * Device-resident state.  With `state` set (and a fused decode step: k_new / v_new given) the lengths and ring
+ * starts of the cache are not taken from this struct but from device memory: state[0..4] = {T, Tkq, Tvq, kf_start,
+ * vf_start} BEFORE the step, state[5] = 0.  The kernel applies upstream's window policy itself
+ * (models/modeling_llama_KVmix.py:115-126: keep `window` tokens, or int(ratio * current_fp16_len)), appends,
+ * quantizes the group that falls due, attends, and leaves state[] describing the cache after the step.  T in this
+ * struct is then only an upper bound used to lay out the grid and the score buffers (any value >= the real length
+ * after the step), Tkq / Tvq / kf_start / vf_start / k_quant* / v_quant* are ignored -- so the same argument block
+ * serves every step and a decode step can be captured once in a CUDA graph and replayed.  At most one group per
+ * step is quantized: use it once the cache is in steady state (a fixed window always is; upstream's ratio policy is
+ * after the first few steps that shrink a prompt's tail).
  */
 
 /*

@@ -65,6 +65,7 @@ class AttnArgs(C.Structure):
                 ("mask", vp), ("mask_sB", i64), ("mask_sH", i64), ("mask_is_f32", i32), ("flags", i32),
                 ("k_new", vp), ("v_new", vp), ("kn_sB", i64), ("kn_sH", i64), ("vn_sB", i64), ("vn_sH", i64),
                 ("k_quant", i32), ("v_quant", i32), ("k_quant_slot", i32), ("v_quant_slot", i32),
+                ("state", vp), ("window", i32), ("k_ratio", C.c_double), ("v_ratio", C.c_double),
                 ("n_peers", i32), ("peer_head0", i32), ("peer_out", vp * 8), ("peer_flag", vp * 8),
                 ("peer_sB", i64), ("peer_sH", i64)]
 

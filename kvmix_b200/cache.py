@@ -40,7 +40,7 @@ def _round_up(x, m):
 
 class KVmixLayerCache:
     def __init__(self, batch, kv_heads, head_dim, max_tokens, k_bits, v_bits, group_size, k_residual_ratio=None,
-                 v_residual_ratio=None, residual_length=None, device="cuda", max_tail=None):
+                 v_residual_ratio=None, residual_length=None, device="cuda", max_tail=None, device_state=False):
         if residual_length is None and (k_residual_ratio is None or v_residual_ratio is None):
             raise ValueError("give residual ratios (upstream policy) or residual_length (fixed window)")
         self.B, self.Hkv, self.D = batch, kv_heads, head_dim
@@ -87,6 +87,10 @@ class KVmixLayerCache:
                              vf.data_ptr(), vf.stride(0), vf.stride(1), vf.stride(2), self.v_cap, 0, 0, 0)
         self._ws = {}
         self._fused = None               # None: not tried yet; False: the library does not fuse this geometry
+        # device_state=True: lengths and ring starts also live in device memory ({T, Tkq, Tvq, k_start, v_start}, then the
+        # grid-completion counter) and fused decode steps read and advance them there; the attributes of this object are
+        # then a host mirror of that state (advance_mirror() moves it along after graph replays)
+        self.state = torch.zeros(8, dtype=torch.int32, device=dev) if device_state else None
         self._lib = _lib.lib()
         self.reset()
 
@@ -95,6 +99,30 @@ class KVmixLayerCache:
         self.k_start = self.k_len = 0    # fp16 key ring
         self.v_start = self.v_len = 0    # fp16 value ring
         self.kv_seq_len = 0
+        self._push_state()
+
+    def _push_state(self):
+        """Host mirror -> device state (after prefill / load / a step made of separate launches)."""
+        if getattr(self, "state", None) is not None:
+            self.state.copy_(torch.tensor([self.kv_seq_len, self.tkq, self.tvq, self.k_start, self.v_start, 0, 0, 0],
+                                          dtype=torch.int32), non_blocking=False)
+
+    def steady(self):
+        """True when the next step quantizes at most one group of keys and of values (what a device-driven step does)."""
+        nk = split_point(self.k_len + 1, self.k_group, self.rk, self.window)
+        nv = split_point(self.v_len + 1, self.v_group, self.rv, self.window)
+        return nk in (0, self.k_group) and nv in (0, self.v_group) and nk <= self.k_len and nv <= self.v_len
+
+    def advance_mirror(self, steps=1):
+        """Move the host mirror along by `steps` device-driven decode steps (e.g. replays of a captured graph)."""
+        for _ in range(steps):
+            nk = split_point(self.k_len + 1, self.k_group, self.rk, self.window)
+            nv = split_point(self.v_len + 1, self.v_group, self.rv, self.window)
+            nk, nv = min(nk, self.k_group), min(nv, self.v_group)
+            self.tkq, self.tvq = self.tkq + nk, self.tvq + nv
+            self.k_start, self.v_start = (self.k_start + nk) % self.k_cap, (self.v_start + nv) % self.v_cap
+            self.k_len, self.v_len = self.k_len + 1 - nk, self.v_len + 1 - nv
+            self.kv_seq_len += 1
 
     # -- cache update --------------------------------------------------------------------------------
     def _quant_k(self, src, n):
@@ -146,6 +174,7 @@ class KVmixLayerCache:
         self.k_start = self.v_start = 0
         self.k_len, self.v_len = L - nk, L - nv
         self.kv_seq_len = L
+        self._push_state()
 
     def prefill_projected(self, k_proj, v_proj, cos=None, sin=None):
         """Prefill straight from the projections (upstream :213-254 plus the rotary embedding before it).
@@ -190,6 +219,7 @@ class KVmixLayerCache:
         self.k_start = self.v_start = 0
         self.k_len, self.v_len = L - nk, L - nv
         self.kv_seq_len = L
+        self._push_state()
 
     def append(self, k_new, v_new):
         """k_new, v_new: [B,Hkv,1,D] fp16.  Upstream decode branch, :111-167."""
@@ -210,6 +240,7 @@ class KVmixLayerCache:
         self.v_len += 1
         self.kv_seq_len += 1
         self._absorb_ring()
+        self._push_state()
 
     # -- attention -----------------------------------------------------------------------------------
     def _workspace(self, nh, stream, device):
@@ -252,19 +283,21 @@ class KVmixLayerCache:
         ops.LAUNCHES[0] += 1
         return out
 
-    def decode_step(self, q, k_new, v_new, out=None, attention_mask=None, round_scores=True, peers=None):
+    def decode_step(self, q, k_new, v_new, out=None, attention_mask=None, round_scores=True, peers=None, plan_tokens=None):
         """Upstream's decode branch for one new token (:105-211): cache update, then attention over everything cached.
         One launch when the library can fuse the update into the attention kernel (one CTA per kv head and segment:
         MHA, or grouped queries with 2 or 4 query heads per kv head, on the tensor-core kernels); otherwise the ring
         append, the group quantizers and the attention are launched one after the other (``append`` + ``attend``)."""
         if self._fused is not False:
-            res = self._decode_step_fused(q, k_new, v_new, out, attention_mask, round_scores, peers)
+            res = self._decode_step_fused(q, k_new, v_new, out, attention_mask, round_scores, peers, plan_tokens)
             if res is not None:
                 return res
+        if plan_tokens is not None:
+            raise RuntimeError("plan_tokens needs a device-driven fused step (device_state=True, steady state, fused geometry)")
         self.append(k_new, v_new)
         return self.attend(q, out=out, attention_mask=attention_mask, round_scores=round_scores, peers=peers)
 
-    def _decode_step_fused(self, q, k_new, v_new, out, attention_mask, round_scores, peers=None):
+    def _decode_step_fused(self, q, k_new, v_new, out, attention_mask, round_scores, peers=None, plan_tokens=None):
         B, nh, M, D = q.shape
         if M != 1 or B != self.B or D != self.D or not q.is_cuda:
             raise RuntimeError("decode_step takes q [B, nh, 1, D] on the cache's device")
@@ -287,19 +320,31 @@ class KVmixLayerCache:
         ws = self._workspace(nh, stream, q.device)
         a = self._att
         a.nh, a.T, a.Tkq, a.Tvq = nh, self.kv_seq_len + 1, self.tkq + nk, self.tvq + nv
+        if self.state is not None:
+            # device-driven: the kernel takes the lengths from self.state and advances them; T only lays out the grid
+            # (plan_tokens: an upper bound valid for every replay of a captured step)
+            if plan_tokens is not None:
+                if plan_tokens < a.T or plan_tokens > self.max_tokens:
+                    raise RuntimeError("plan_tokens must cover the step and fit the cache")
+                if attention_mask is not None:
+                    raise RuntimeError("a step planned for later lengths cannot carry a mask of a fixed length")
+                a.T = int(plan_tokens)
+            a.state = self.state.data_ptr()
+            a.window = -1 if self.window is None else int(self.window)
+            a.k_ratio, a.v_ratio = float(self.rk or 0.0), float(self.rv or 0.0)
         a.round_scores = int(bool(round_scores))
         a.q, a.q_sB, a.q_sH = q.data_ptr(), q.stride(0), q.stride(1)
         a.out, a.o_sB, a.o_sH = out.data_ptr(), out.stride(0), out.stride(1)
         a.kf_start, a.vf_start = (self.k_start + nk) % self.k_cap, (self.v_start + nv) % self.v_cap
         a.workspace, a.workspace_bytes, a.flags = ws.data_ptr(), ws.numel(), _lib.ATTN_WORKSPACE_READY
-        a.mask, a.mask_sB, a.mask_sH, a.mask_is_f32 = ops.mask_fields(attention_mask, B, nh, a.T)
+        a.mask, a.mask_sB, a.mask_sH, a.mask_is_f32 = ops.mask_fields(attention_mask, B, nh, self.kv_seq_len + 1)
         a.k_new, a.kn_sB, a.kn_sH = k_new.data_ptr(), k_new.stride(0), k_new.stride(1)
         a.v_new, a.vn_sB, a.vn_sH = v_new.data_ptr(), v_new.stride(0), v_new.stride(1)
         a.k_quant, a.v_quant, a.k_quant_slot, a.v_quant_slot = nk, nv, self.k_start, self.v_start
         if peers is not None:
             peers.fill(a)
         rc = self._lib.kvq_decode_attn(C.byref(a), C.c_void_p(stream))
-        a.k_new = a.v_new = None
+        a.k_new = a.v_new = a.state = None
         a.k_quant = a.v_quant = a.n_peers = 0
         if rc == -11:                                           # this geometry is not served fused: remember and fall back
             self._fused = False
@@ -373,6 +418,7 @@ class KVmixLayerCache:
         if self.tkq + self.k_len != self.kv_seq_len or self.tvq + self.v_len != self.kv_seq_len:
             self.reset()
             raise RuntimeError("inconsistent token counts")
+        self._push_state()
 
     def packed_bytes(self):
         """Bytes one attend() must read: codes + scale/zero + fp16 tails (the roofline numerator)."""

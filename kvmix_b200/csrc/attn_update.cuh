@@ -119,6 +119,51 @@ __device__ __forceinline__ const __half *v_tail_row(const kvq_attn_args &a, cons
     return vf + (int64_t)s * a.vf_sT;
 }
 
+// Device-resident cache state (kvq_attn_args.state): five ints {T, Tkq, Tvq, kf_start, vf_start} describing the cache
+// BEFORE this step, a completion counter at [5].  The kernel applies upstream's window policy itself -- keep
+// `window` tokens in fp16, or int(ratio * current_fp16_len) (models/modeling_llama_KVmix.py:118-126) -- to derive
+// what this step does, and the CTA that finishes last writes the state after the step back, so the launch arguments
+// of a decode loop never change and a whole step can be replayed from a CUDA graph.  At most one group per step
+// becomes due in steady state; the host does not switch to this mode before that (upstream's ratio policy shrinks a
+// prompt's tail over several steps).
+__device__ __forceinline__ int tokens_due(const kvq_attn_args &a, int cur, int group, double ratio) {
+    const int keep = a.window >= 0 ? a.window : (int)(ratio * (double)cur);
+    if (cur > keep && keep >= 0) {
+        const int n = ((cur - keep) / group) * group;
+        return n > group ? group : n;
+    }
+    return 0;
+}
+
+__device__ __forceinline__ void dev_state_step(const kvq_attn_args &a, kvq_attn_args &b) {
+    const int *st = a.state;
+    const int T0 = st[0], Tkq0 = st[1], Tvq0 = st[2], ks0 = st[3], vs0 = st[4];
+    const int nk = tokens_due(a, T0 - Tkq0 + 1, a.k_group, a.k_ratio);
+    const int nv = tokens_due(a, T0 - Tvq0 + 1, a.v_group, a.v_ratio);
+    b.T = T0 + 1;
+    b.Tkq = Tkq0 + nk;
+    b.Tvq = Tvq0 + nv;
+    b.kf_start = ks0 + nk >= a.kf_cap ? ks0 + nk - a.kf_cap : ks0 + nk;
+    b.vf_start = vs0 + nv >= a.vf_cap ? vs0 + nv - a.vf_cap : vs0 + nv;
+    b.k_quant = nk;
+    b.v_quant = nv;
+    b.k_quant_slot = ks0;
+    b.v_quant_slot = vs0;
+}
+
+// Every CTA calls this as its last action; the last one to arrive publishes the state after the step.
+__device__ __forceinline__ void dev_state_commit(const kvq_attn_args &b, int tid) {
+    __syncthreads();
+    if (tid == 0) {
+        int *st = b.state;
+        __threadfence();
+        if (atomicAdd(reinterpret_cast<unsigned int *>(st + 5), 1u) == gridDim.x - 1) {
+            st[0] = b.T; st[1] = b.Tkq; st[2] = b.Tvq; st[3] = b.kf_start; st[4] = b.vf_start;
+            st[5] = 0;
+        }
+    }
+}
+
 // Head-sharded exchange: the rows `vals[i]` (this thread's channel `tid` of `n_heads` consecutive query heads starting
 // at local head h0 of sequence b) go to every rank's gather buffer, then every rank's arrival counter is raised by
 // n_heads.  Every thread of the CTA calls it (CTA barrier inside).  Plain peer stores and one system-scope

@@ -401,9 +401,14 @@ extern "C" int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream) {
     if (!a->q || !a->out) return KVQ_ERR_NULL;
     if (a->Tkq > 0 && (!a->kcode || !a->kscale || !a->kmn)) return KVQ_ERR_NULL;
     if (a->Tvq > 0 && (!a->vcode || !a->vscale || !a->vmn)) return KVQ_ERR_NULL;
+    const bool dev_state = a->state != nullptr;                // lengths live on the device: T here is only an upper bound
     const int Rk = a->T - a->Tkq, Rv = a->T - a->Tvq;
-    if (Rk > 0 && (!a->kfull || a->kf_cap < Rk || a->kf_start < 0 || a->kf_start >= a->kf_cap)) return KVQ_ERR_SHAPE;
-    if (Rv > 0 && (!a->vfull || a->vf_cap < Rv || a->vf_start < 0 || a->vf_start >= a->vf_cap)) return KVQ_ERR_SHAPE;
+    if (!dev_state && Rk > 0 && (!a->kfull || a->kf_cap < Rk || a->kf_start < 0 || a->kf_start >= a->kf_cap)) return KVQ_ERR_SHAPE;
+    if (!dev_state && Rv > 0 && (!a->vfull || a->vf_cap < Rv || a->vf_start < 0 || a->vf_start >= a->vf_cap)) return KVQ_ERR_SHAPE;
+    if (dev_state && (!a->k_new || !a->kfull || !a->vfull || !a->kcode || !a->vcode || !a->kscale || !a->vscale || !a->kmn || !a->vmn))
+        return KVQ_ERR_NULL;                                   // device-resident state comes with the fused decode step
+    if (dev_state && a->window < 0 && !(a->k_ratio >= 0.0 && a->k_ratio < 1.0 && a->v_ratio >= 0.0 && a->v_ratio < 1.0))
+        return KVQ_ERR_SHAPE;
     if (Rk > 0 && (reinterpret_cast<uintptr_t>(a->kfull) % 8 || a->kf_sB % 4 || a->kf_sH % 4 || a->kf_sT % 4))
         return KVQ_ERR_ALIGN;
     if (Rv > 0 && (reinterpret_cast<uintptr_t>(a->vfull) % 4 || a->vf_sB % 2 || a->vf_sH % 2 || a->vf_sT % 2))
@@ -421,11 +426,15 @@ extern "C" int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream) {
         if (!a->k_new || !a->v_new) return KVQ_ERR_NULL;
         const int n_rep = a->nh / a->nh_kv;
         if (!L.use_mma || (L.qhv ? n_rep != L.qhv : n_rep != 1)) return KVQ_ERR_UNSUPPORTED;   // one CTA per kv head and segment
-        if (Rk < 1 || Rv < 1) return KVQ_ERR_TOKENS;           // the new token stays in the fp16 tails
-        if ((a->k_quant != 0 && a->k_quant != a->k_group) || (a->v_quant != 0 && a->v_quant != a->v_group)) return KVQ_ERR_TOKENS;
-        if (a->k_quant > a->Tkq || a->v_quant > a->Tvq) return KVQ_ERR_TOKENS;
-        if (a->k_quant && (a->k_quant_slot < 0 || a->k_quant_slot + a->k_quant > a->kf_cap)) return KVQ_ERR_SHAPE;
-        if (a->v_quant && (a->v_quant_slot < 0 || a->v_quant_slot + a->v_quant > a->vf_cap)) return KVQ_ERR_SHAPE;
+        if (!dev_state) {
+            if (Rk < 1 || Rv < 1) return KVQ_ERR_TOKENS;       // the new token stays in the fp16 tails
+            if ((a->k_quant != 0 && a->k_quant != a->k_group) || (a->v_quant != 0 && a->v_quant != a->v_group)) return KVQ_ERR_TOKENS;
+            if (a->k_quant > a->Tkq || a->v_quant > a->Tvq) return KVQ_ERR_TOKENS;
+            if (a->k_quant && (a->k_quant_slot < 0 || a->k_quant_slot + a->k_quant > a->kf_cap)) return KVQ_ERR_SHAPE;
+            if (a->v_quant && (a->v_quant_slot < 0 || a->v_quant_slot + a->v_quant > a->vf_cap)) return KVQ_ERR_SHAPE;
+        } else if (a->kf_cap % a->k_group != 0 || a->vf_cap % a->v_group != 0) {
+            return KVQ_ERR_SHAPE;                              // a group must not wrap around its ring
+        }
         auto bad = [](const void *p, int64_t s0, int64_t s1) { return reinterpret_cast<uintptr_t>(p) % 16 != 0 || s0 % 8 != 0 || s1 % 8 != 0; };
         if (bad(a->k_new, a->kn_sB, a->kn_sH) || bad(a->v_new, a->vn_sB, a->vn_sH)) return KVQ_ERR_ALIGN;
     }

@@ -729,14 +729,23 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, int n_scores
     peer_publish(a, b, h_first, qhv, res, tid);
 }
 
-template <int KB, int VB>
+template <int KB, int VB, bool DEV>
 __global__ void __launch_bounds__(kMmaThreads, 2) decode_attn_gqa_kernel(const __grid_constant__ kvq_attn_args a,
                                                                      const __grid_constant__ AttnPlan plan, int qhv,
                                                                      float *__restrict__ parts,
                                                                      unsigned int *__restrict__ counters) {
     int group, t0, t1, seg, cnt;
-    plan_cta(plan, a.T, blockIdx.x, group, t0, t1, seg, cnt);
-    gqa_segment<KB, VB>(a, plan.n_scores, qhv, group, t0, t1, seg, cnt, plan.n_whole, parts, counters);
+    if constexpr (DEV) {                                       // device-resident cache state: see decode_attn_mma_kernel
+        kvq_attn_args b = a;
+        dev_state_step(a, b);
+        plan_cta(plan, b.T, blockIdx.x, group, t0, t1, seg, cnt);
+        if (cnt > 1) cnt = min(cnt, (b.T + plan.seg_units * plan.unit - 1) / (plan.seg_units * plan.unit));
+        if (t0 < b.T) gqa_segment<KB, VB>(b, plan.n_scores, qhv, group, t0, t1, seg, cnt, plan.n_whole, parts, counters);
+        dev_state_commit(b, threadIdx.x);
+    } else {
+        plan_cta(plan, a.T, blockIdx.x, group, t0, t1, seg, cnt);
+        gqa_segment<KB, VB>(a, plan.n_scores, qhv, group, t0, t1, seg, cnt, plan.n_whole, parts, counters);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -770,11 +779,15 @@ static int launch_gqa(const kvq_attn_args &a, const AttnPlan &plan, int qhv, flo
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return record_cuda_error(e);
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        e = cudaFuncSetAttribute(decode_attn_gqa_kernel<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+        e = cudaFuncSetAttribute(decode_attn_gqa_kernel<KB, VB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(decode_attn_gqa_kernel<KB, VB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
         if (e != cudaSuccess) return record_cuda_error(e);
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    decode_attn_gqa_kernel<KB, VB><<<(unsigned)(plan.n_whole + plan.n_cut * plan.k), kMmaThreads, smem, st>>>(a, plan, qhv, parts, counters);
+    const unsigned grid = (unsigned)(plan.n_whole + plan.n_cut * plan.k);
+    if (a.state) decode_attn_gqa_kernel<KB, VB, true><<<grid, kMmaThreads, smem, st>>>(a, plan, qhv, parts, counters);
+    else decode_attn_gqa_kernel<KB, VB, false><<<grid, kMmaThreads, smem, st>>>(a, plan, qhv, parts, counters);
     return check_launch();
 }
 

@@ -784,14 +784,25 @@ __device__ __forceinline__ void attn_segment(const kvq_attn_args &a, int n_score
 }
 
 // CTA = one segment (see attn_plan.cuh): a whole head, or one of the k pieces of a head that is cut.
-template <int KB, int VB>
+// DEV: lengths and ring starts come from the device-resident state (attn_update.cuh); the plan was laid out for an
+// upper bound of the length, so segments beyond the real length are empty and a head counts fewer of them.
+template <int KB, int VB, bool DEV>
 __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(const __grid_constant__ kvq_attn_args a,
                                                                      const __grid_constant__ AttnPlan plan,
                                                                      float *__restrict__ parts,
                                                                      unsigned int *__restrict__ counters) {
     int head, t0, t1, seg, cnt;
-    plan_cta(plan, a.T, blockIdx.x, head, t0, t1, seg, cnt);
-    attn_segment<KB, VB>(a, plan.n_scores, head, t0, t1, seg, cnt, plan.n_whole, parts, counters);
+    if constexpr (DEV) {
+        kvq_attn_args b = a;
+        dev_state_step(a, b);
+        plan_cta(plan, b.T, blockIdx.x, head, t0, t1, seg, cnt);
+        if (cnt > 1) cnt = min(cnt, (b.T + plan.seg_units * plan.unit - 1) / (plan.seg_units * plan.unit));
+        if (t0 < b.T) attn_segment<KB, VB>(b, plan.n_scores, head, t0, t1, seg, cnt, plan.n_whole, parts, counters);
+        dev_state_commit(b, threadIdx.x);
+    } else {
+        plan_cta(plan, a.T, blockIdx.x, head, t0, t1, seg, cnt);
+        attn_segment<KB, VB>(a, plan.n_scores, head, t0, t1, seg, cnt, plan.n_whole, parts, counters);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -832,11 +843,15 @@ static int launch_mma(const kvq_attn_args &a, const AttnPlan &plan, float *parts
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return record_cuda_error(e);
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        e = cudaFuncSetAttribute(decode_attn_mma_kernel<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+        e = cudaFuncSetAttribute(decode_attn_mma_kernel<KB, VB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(decode_attn_mma_kernel<KB, VB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
         if (e != cudaSuccess) return record_cuda_error(e);
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    decode_attn_mma_kernel<KB, VB><<<(unsigned)(plan.n_whole + plan.n_cut * plan.k), kMmaThreads, smem, st>>>(a, plan, parts, counters);
+    const unsigned grid = (unsigned)(plan.n_whole + plan.n_cut * plan.k);
+    if (a.state) decode_attn_mma_kernel<KB, VB, true><<<grid, kMmaThreads, smem, st>>>(a, plan, parts, counters);
+    else decode_attn_mma_kernel<KB, VB, false><<<grid, kMmaThreads, smem, st>>>(a, plan, parts, counters);
     return check_launch();
 }
 
