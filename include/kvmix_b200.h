@@ -75,6 +75,12 @@ int kvq_features_per_int(int bits);
  *   scale_by_division = 0: (max-min) * fl32(1/(2^b-1)), what quantize_pack_last_dim_cuda returns
  *       (its torch-side "tensor / scalar" at :711 is evaluated as a multiplication by the reciprocal);
  *   scale_by_division = 1: (max-min) / (2^b-1), what the upstream append kernels store (:51-53, :232-234).
+ *
+ * EXTENSION WITHOUT AN UPSTREAM COUNTERPART (nothing upstream pins it): ragged_tail != 0 with bits == 3 lifts the
+ * S % 11 == 0 rule.  code, scale and mn then have ceil(S/11) entries per row: groups of 11 with a last group of
+ * S % 11 elements, each group one word, unused fields 0, upstream's 3-bit group rule otherwise (element 10 of a full
+ * group keeps its 2-bit field).  It exists for 3-bit *values* at head_dim 128 (12 words per token, the last holding 7
+ * codes), which upstream cannot represent (:433-434).  kvq_decode_attn reads that layout when v_bits == 3.
  */
 typedef struct {
     const void *x;
@@ -88,6 +94,7 @@ typedef struct {
     void *scale;
     void *mn;
     int64_t z_sB, z_sH, z_sA;
+    int32_t ragged_tail;                /* extension, see below; 0 = upstream's rules */
 } kvq_quant_args;
 
 int kvq_quant_lastdim(const kvq_quant_args *a, kvq_stream_t stream);
@@ -250,7 +257,10 @@ int kvq_gemv(const kvq_gemv_args *a, kvq_stream_t stream);
  * rows contiguous: vc_sT == D/fpi_v, vs_sT == D/v_group) -- what a preallocated cache provides.  Anything else runs
  * on a slower CUDA-core kernel with the same results.
  * D must be 128.  k_group and v_group must be multiples of the fields per word (k_group == 11 for
- * 3-bit keys); 3-bit values need D % 11 == 0 upstream and are rejected here for D = 128.
+ * 3-bit keys).  3-bit values (v_bits == 3, v_group == 11) are an extension without an upstream counterpart --
+ * upstream needs D % 11 == 0 for them (quant_cuda/csrc/quantization_cuda.cu:433-434) -- in the layout
+ * kvq_quant_lastdim writes with ragged_tail: vcode [B, nh_kv, Tvq, 12], vscale / vmn [B, nh_kv, Tvq, 12], word j
+ * holding channels 11j .. min(11j + 10, 127) as its own group; they run on the CUDA-core kernel.
  * round_scores != 0 narrows each raw score to fp16 before scaling, as upstream's GEMV and fp16
  * matmul do; everything else accumulates in fp32.
  *

@@ -18,7 +18,7 @@ class QuantArgs(C.Structure):
                 ("x_sB", i64), ("x_sH", i64), ("x_sA", i64), ("x_sS", i64),
                 ("group", i32), ("bits", i32), ("scale_by_division", i32),
                 ("code", vp), ("c_sB", i64), ("c_sH", i64), ("c_sA", i64),
-                ("scale", vp), ("mn", vp), ("z_sB", i64), ("z_sH", i64), ("z_sA", i64)]
+                ("scale", vp), ("mn", vp), ("z_sB", i64), ("z_sH", i64), ("z_sA", i64), ("ragged_tail", i32)]
 
 
 class GemvArgs(C.Structure):

@@ -45,8 +45,11 @@ class KVmixLayerCache:
             raise ValueError("give residual ratios (upstream policy) or residual_length (fixed window)")
         self.B, self.Hkv, self.D = batch, kv_heads, head_dim
         self.k_bits, self.v_bits = k_bits, v_bits
-        self.v_group = group_size
+        self.v_group = group_size                               # values are quantized group_size tokens at a time
         self.k_group = 11 if k_bits == 3 else group_size       # modeling_llama_KVmix.py:49-52
+        # channel groups of the values.  3-bit values are an extension upstream does not have (its 3-bit rule needs
+        # head_dim % 11 == 0, quantization_cuda.cu:433-434): groups of 11 channels, one word each, the last one short
+        self.v_cgroup = 11 if v_bits == 3 else group_size
         self.rk, self.rv, self.window = k_residual_ratio, v_residual_ratio, residual_length
         self.fk, self.fv = features_per_int(k_bits), features_per_int(v_bits)
         max_tokens = _round_up(max_tokens, 32)                  # keeps every per-head base 16-byte aligned
@@ -58,8 +61,8 @@ class KVmixLayerCache:
         self.kcode = torch.empty((B, H, D, kw), dtype=torch.int32, device=dev)
         self.kscale = torch.empty((B, H, D, kg), dtype=torch.float16, device=dev)
         self.kmn = torch.empty_like(self.kscale)
-        self.vcode = torch.empty((B, H, max_tokens, D // self.fv), dtype=torch.int32, device=dev)
-        self.vscale = torch.empty((B, H, max_tokens, D // self.v_group), dtype=torch.float16, device=dev)
+        self.vcode = torch.empty((B, H, max_tokens, -(-D // self.fv)), dtype=torch.int32, device=dev)
+        self.vscale = torch.empty((B, H, max_tokens, -(-D // self.v_cgroup)), dtype=torch.float16, device=dev)
         self.vmn = torch.empty_like(self.vscale)
         if max_tail is None:
             if residual_length is not None:
@@ -77,7 +80,7 @@ class KVmixLayerCache:
         self._app = AppendArgs(B, H, D, 0, 0, 0, 0, 0, 0, kf.data_ptr(), kf.stride(0), kf.stride(1), kf.stride(2), 0,
                                vf.data_ptr(), vf.stride(0), vf.stride(1), vf.stride(2), 0)
         kc, ks, vc, vs = self.kcode, self.kscale, self.vcode, self.vscale
-        self._att = AttnArgs(B, 0, H, D, 0, 0, 0, k_bits, self.k_group, v_bits, self.v_group, 1, 1.0 / math.sqrt(D),
+        self._att = AttnArgs(B, 0, H, D, 0, 0, 0, k_bits, self.k_group, v_bits, self.v_cgroup, 1, 1.0 / math.sqrt(D),
                              0, 0, 0, 0, 0, 0,
                              kc.data_ptr(), kc.stride(0), kc.stride(1), kc.stride(2),
                              ks.data_ptr(), self.kmn.data_ptr(), ks.stride(0), ks.stride(1), ks.stride(2),
@@ -135,8 +138,8 @@ class KVmixLayerCache:
 
     def _quant_v(self, src, n):
         t0 = self.tvq
-        ops.quantize_into(src, self.v_group, self.v_bits, self.vcode[:, :, t0:t0 + n], self.vscale[:, :, t0:t0 + n],
-                          self.vmn[:, :, t0:t0 + n])
+        ops.quantize_into(src, self.v_cgroup, self.v_bits, self.vcode[:, :, t0:t0 + n], self.vscale[:, :, t0:t0 + n],
+                          self.vmn[:, :, t0:t0 + n], ragged_tail=self.v_bits == 3)
         self.tvq += n
 
     def _absorb_ring(self):
@@ -205,7 +208,7 @@ class KVmixLayerCache:
             a.cos, a.sin = cos.data_ptr(), sin.data_ptr()
             a.r_sB, a.r_sT = (c3.stride(0) if c3.shape[0] == B and B > 1 else 0), c3.stride(1)
         a.B, a.Hkv, a.L, a.D, a.nk, a.nv = B, self.Hkv, L, self.D, nk, nv
-        a.k_bits, a.k_group, a.v_bits, a.v_group = self.k_bits, self.k_group, self.v_bits, self.v_group
+        a.k_bits, a.k_group, a.v_bits, a.v_group = self.k_bits, self.k_group, self.v_bits, self.v_cgroup
         kc, ks, vc, vs, kf, vf = self.kcode, self.kscale, self.vcode, self.vscale, self.kfull, self.vfull
         a.kcode, a.kc_sB, a.kc_sH, a.kc_sD = kc.data_ptr(), kc.stride(0), kc.stride(1), kc.stride(2)
         a.kscale, a.kmn, a.ks_sB, a.ks_sH, a.ks_sD = ks.data_ptr(), self.kmn.data_ptr(), ks.stride(0), ks.stride(1), ks.stride(2)
@@ -423,7 +426,7 @@ class KVmixLayerCache:
     def packed_bytes(self):
         """Bytes one attend() must read: codes + scale/zero + fp16 tails (the roofline numerator)."""
         per_head = kv_bytes_per_head(self.tkq, self.tvq, self.k_len, self.v_len, self.D, self.k_bits, self.k_group,
-                                     self.v_bits, self.v_group)
+                                     self.v_bits, self.v_cgroup)
         return per_head * self.B * self.Hkv
 
 
@@ -432,8 +435,8 @@ def kv_bytes_per_head(tkq, tvq, rk, rv, D, k_bits, k_group, v_bits, v_group):
     fk, fv = features_per_int(k_bits), features_per_int(v_bits)
     kcodes = (tkq // fk) * 4 * D
     ksz = (tkq // k_group) * D * 4
-    vcodes = tvq * (D // fv) * 4
-    vsz = tvq * (D // v_group) * 4
+    vcodes = tvq * -(-D // fv) * 4                             # ceil: 3-bit values hold 12 words / groups per token
+    vsz = tvq * -(-D // v_group) * 4
     resid = (rk + rv) * D * 2
     return kcodes + ksz + vcodes + vsz + resid
 

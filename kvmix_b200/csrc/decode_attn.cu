@@ -111,6 +111,36 @@ __device__ __forceinline__ void pv_packed(const kvq_attn_args &a, const int32_t 
     }
 }
 
+// 3-bit values, an extension upstream does not have (its 3-bit rule needs head_dim % 11 == 0): 12 words per token
+// row, word j holding channels 11j .. min(11j + 10, 127) and being its own group (scale/zero j).  16 lane slots per
+// token of which 12 work, 16 tokens per pass.
+__device__ __forceinline__ void pv_packed3(const kvq_attn_args &a, const int32_t *vc, const __half *vs,
+                                           const __half *vz, Smem &sm, int t0, int lo, int hi) {
+    constexpr int WPT = (kHeadDim + 10) / 11;
+    const int j = threadIdx.x & 15, tl = threadIdx.x >> 4;
+    float acc[11];
+#pragma unroll
+    for (int i = 0; i < 11; ++i) acc[i] = 0.f;
+    float zacc = 0.f;
+    if (j < WPT) {
+        for (int t = lo + tl; t < hi; t += kAttnThreads / 16) {
+            const uint32_t word = (uint32_t)__ldg(vc + (int64_t)t * a.vc_sT + j);
+            const float p = sm.scores[t - t0];
+            const float ps = p * __half2float(__ldg(vs + (int64_t)t * a.vs_sT + j));
+            zacc = fmaf(p, __half2float(__ldg(vz + (int64_t)t * a.vs_sT + j)), zacc);
+#pragma unroll
+            for (int i = 0; i < 11; ++i) acc[i] = fmaf(ps, (float)field<3>(word, i), acc[i]);
+        }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < 11; ++i) {
+        float v = acc[i] + zacc;
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        if (lane < WPT && j * 11 + i < kHeadDim) sm.red[warp][j * 11 + i] = v;
+    }
+}
+
 __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(kvq_attn_args a, int chunk, int n_splits,
                                                                   float *__restrict__ parts,
                                                                   unsigned int *__restrict__ counters) {
@@ -211,6 +241,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(kvq_attn_args
             switch (a.v_bits) {
                 case 1: pv_packed<1>(a, vc, vs, vz, sm, t0, t0, hi); break;
                 case 2: pv_packed<2>(a, vc, vs, vz, sm, t0, t0, hi); break;
+                case 3: pv_packed3(a, vc, vs, vz, sm, t0, t0, hi); break;
                 default: pv_packed<4>(a, vc, vs, vz, sm, t0, t0, hi); break;
             }
         }
@@ -394,10 +425,10 @@ extern "C" int kvq_decode_attn(const kvq_attn_args *a, kvq_stream_t stream) {
     if (a->k_bits < 1 || a->k_bits > 4 || a->v_bits < 1 || a->v_bits > 4) return KVQ_ERR_BITS;
     const int fk = fields_per_word(a->k_bits), fv = fields_per_word(a->v_bits);
     if (a->k_bits == 3 && a->k_group != 11) return KVQ_ERR_GROUP3;
-    if (a->v_bits == 3) return KVQ_ERR_UNSUPPORTED;  // upstream cannot hold 3-bit values for D = 128 either
+    if (a->v_bits == 3 && a->v_group != 11) return KVQ_ERR_GROUP3;   // 3-bit values: the short-last-group extension layout
     if (a->k_group <= 0 || a->k_group % fk != 0 || a->v_group <= 0 || a->v_group % fv != 0) return KVQ_ERR_GROUPWORD;
     if (a->Tkq % a->k_group != 0) return KVQ_ERR_DIVGROUP;
-    if (kHeadDim % a->v_group != 0) return KVQ_ERR_DIVGROUP;
+    if (a->v_bits != 3 && kHeadDim % a->v_group != 0) return KVQ_ERR_DIVGROUP;
     if (!a->q || !a->out) return KVQ_ERR_NULL;
     if (a->Tkq > 0 && (!a->kcode || !a->kscale || !a->kmn)) return KVQ_ERR_NULL;
     if (a->Tvq > 0 && (!a->vcode || !a->vscale || !a->vmn)) return KVQ_ERR_NULL;

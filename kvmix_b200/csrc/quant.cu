@@ -276,6 +276,46 @@ __global__ void __launch_bounds__(128) quant_generic_kernel(const T *__restrict_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Extension without an upstream counterpart: 3-bit groups of 11 along an axis whose length is not a multiple of 11
+// (3-bit values at head_dim 128).  Every group is one word; the last group holds S % 11 elements, its unused fields
+// stay 0.  Upstream's 3-bit group rule otherwise (quantization_cuda.cu:553-596, :612-626).  One thread per word.
+template <typename T>
+__global__ void __launch_bounds__(128) quant_ragged3_kernel(const T *__restrict__ x, int32_t *__restrict__ code,
+                                                            T *__restrict__ scale, T *__restrict__ mn, QuantDims d) {
+    const int64_t words_per_row = (d.S + 10) / 11;
+    const int64_t total = d.B * d.H * d.A * words_per_row;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t row = idx / words_per_row, w = idx % words_per_row;
+    const int64_t a = row % d.A, h = (row / d.A) % d.H, b = row / (d.A * d.H);
+    const T *px = x + b * d.x_sB + h * d.x_sH + a * d.x_sA + w * 11 * d.x_sS;
+    const int n = (int)min((int64_t)11, d.S - w * 11);
+    float v[11], lo = 3.402823466e+38f, hi = -3.402823466e+38f;
+#pragma unroll
+    for (int i = 0; i < 11; ++i) {
+        v[i] = i < n ? to_f32<T>(px[i * d.x_sS]) : 0.f;
+        if (i < n) { lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]); }
+    }
+    const float range = hi - lo, sc = range / 7.0f;
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < 11; ++i)
+        if (i < n) word |= (uint32_t)round_code((v[i] - lo) / sc, i < 10 ? 7 : 3) << (i < 10 ? 3 * i : 30);
+    code[b * d.c_sB + h * d.c_sH + a * d.c_sA + w] = (int32_t)word;
+    const int64_t zo = b * d.z_sB + h * d.z_sH + a * d.z_sA + w;
+    scale[zo] = from_f32<T>(stored_scale<7>(range, sc, d.by_div));
+    mn[zo] = from_f32<T>(lo);
+}
+
+template <typename T>
+static int launch_ragged3(const kvq_quant_args *a, const QuantDims &d, cudaStream_t st) {
+    const int64_t total = d.B * d.H * d.A * ((d.S + 10) / 11);
+    quant_ragged3_kernel<T><<<(unsigned)((total + 127) / 128), 128, 0, st>>>(
+        static_cast<const T *>(a->x), a->code, static_cast<T *>(a->scale), static_cast<T *>(a->mn), d);
+    return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------
 template <int BITS, typename T>
 static int launch_bits(const kvq_quant_args *a, const QuantDims &d, cudaStream_t st, const RopeTables *rope = nullptr) {
     constexpr int E = fields_per_word(BITS);
@@ -352,13 +392,20 @@ static int kvq::quant_lastdim_impl(const kvq_quant_args *a, kvq_stream_t stream,
     if (a->B < 0 || a->H < 0 || a->A < 0 || a->S < 0) return KVQ_ERR_SHAPE;
     if (a->bits == 3) {
         if (a->group != 11) return KVQ_ERR_GROUP3;
-        if (a->S % 11 != 0) return KVQ_ERR_DIV11;
+        if (a->S % 11 != 0 && !a->ragged_tail) return KVQ_ERR_DIV11;
     } else {
         if (a->group <= 0 || a->S % a->group != 0) return KVQ_ERR_DIVGROUP;
         if (a->S % (32 / a->bits) != 0) return KVQ_ERR_DIVWORD;
     }
     if (a->B * a->H * a->A * a->S == 0) return KVQ_OK;
     if (!a->x || !a->code || !a->scale || !a->mn) return KVQ_ERR_NULL;
+    if (a->bits == 3 && a->S % 11 != 0) {                      // the short-last-group extension
+        if (rope) return KVQ_ERR_UNSUPPORTED;
+        QuantDims r{a->B, a->H, a->A, a->S, a->x_sB, a->x_sH, a->x_sA, a->x_sS, a->c_sB, a->c_sH, a->c_sA,
+                    a->z_sB, a->z_sH, a->z_sA, 11, a->scale_by_division ? 1 : 0};
+        cudaStream_t rs = reinterpret_cast<cudaStream_t>(stream);
+        return a->x_is_f32 ? launch_ragged3<float>(a, r, rs) : launch_ragged3<__half>(a, r, rs);
+    }
     QuantDims d{a->B, a->H, a->A, a->S, a->x_sB, a->x_sH, a->x_sA, a->x_sS, a->c_sB, a->c_sH, a->c_sA,
                 a->z_sB, a->z_sH, a->z_sA, a->group, a->scale_by_division ? 1 : 0};
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -530,7 +577,8 @@ extern "C" int kvq_prefill(const kvq_prefill_args *a, kvq_stream_t stream) {
     }
     if (a->nv > 0) {                                           // values: groups over channels
         kvq_quant_args q{a->v, 0, a->B, a->Hkv, a->nv, a->D, a->v_sB, a->v_sH, a->v_sT, 1, a->v_group, a->v_bits, 0,
-                         a->vcode, a->vc_sB, a->vc_sH, a->vc_sT, a->vscale, a->vmn, a->vs_sB, a->vs_sH, a->vs_sT};
+                         a->vcode, a->vc_sB, a->vc_sH, a->vc_sT, a->vscale, a->vmn, a->vs_sB, a->vs_sH, a->vs_sT,
+                         a->v_bits == 3 ? 1 : 0};               // 3-bit values: the short-last-group extension
         const int rc = kvq_quant_lastdim(&q, stream);
         if (rc) return rc;
     }

@@ -53,13 +53,15 @@ def _check_quant_rules(S, group_length, quant_bits):
             check(-5)
 
 
-def quantize_into(x, group_length, quant_bits, code, scale, mn, scale_by_division=False):
+def quantize_into(x, group_length, quant_bits, code, scale, mn, scale_by_division=False, ragged_tail=False):
     """Quantize 4-D ``x`` (any strides) along its last dim into preallocated views.
 
     ``code`` [B,H,A,S/fpi] int32, ``scale``/``mn`` [B,H,A,S/G] (dtype of x); their last dim must be
     contiguous, other strides are free, so they may be slices of a larger cache.
     ``scale_by_division`` selects how the stored scale is rounded (see include/kvmix_b200.h): False
     reproduces quantize_pack_last_dim_cuda, True the upstream append kernels.
+    ``ragged_tail`` (an extension upstream does not have, 3 bits only): S need not be a multiple of 11; outputs
+    hold ceil(S/11) words / groups per row, the last group being short.
     """
     _need_cuda(x, code, scale, mn)
     if x.dim() != 4:
@@ -67,11 +69,14 @@ def quantize_into(x, group_length, quant_bits, code, scale, mn, scale_by_divisio
     if x.dtype not in (torch.float16, torch.float32):
         raise RuntimeError("input must be float16 or float32")
     B, H, A, S = x.shape
-    _check_quant_rules(S, group_length, quant_bits)
+    ragged = bool(ragged_tail) and quant_bits == 3 and group_length == 11 and S % 11 != 0
+    if not ragged:
+        _check_quant_rules(S, group_length, quant_bits)
     fpi = features_per_int(quant_bits)
-    assert code.dtype == torch.int32 and tuple(code.shape) == (B, H, A, S // fpi)
+    nw, ng = (-(-S // 11), -(-S // 11)) if ragged else (S // fpi, S // group_length)
+    assert code.dtype == torch.int32 and tuple(code.shape) == (B, H, A, nw)
     assert scale.dtype == x.dtype and mn.dtype == x.dtype
-    assert tuple(scale.shape) == (B, H, A, S // group_length) == tuple(mn.shape)
+    assert tuple(scale.shape) == (B, H, A, ng) == tuple(mn.shape)
     assert scale.stride() == mn.stride()
     if x.numel() == 0:
         return
@@ -79,7 +84,7 @@ def quantize_into(x, group_length, quant_bits, code, scale, mn, scale_by_divisio
     a = QuantArgs(x.data_ptr(), int(x.dtype == torch.float32), B, H, A, S, x.stride(0), x.stride(1), x.stride(2),
                   x.stride(3), group_length, quant_bits, int(bool(scale_by_division)), code.data_ptr(), code.stride(0), code.stride(1),
                   code.stride(2), scale.data_ptr(), mn.data_ptr(), scale.stride(0), scale.stride(1),
-                  scale.stride(2))
+                  scale.stride(2), int(ragged))
     check(_lib.lib().kvq_quant_lastdim(C.byref(a), _stream()))
     LAUNCHES[0] += 1
 

@@ -96,6 +96,23 @@ def quantize_pack_last_dim(x, group_length, quant_bits):
     return code, scale, mn
 
 
+def quantize_ragged3(x, scale_by_division=False):
+    """EXTENSION (no upstream counterpart, parity unpinned): 3-bit groups of 11 along the last axis with a short last
+    group, for rows whose length is not a multiple of 11 (3-bit values at head_dim 128: 12 words per token, the last
+    one holding 7 codes).  x [B,H,A,S] fp16 -> code int32, scale, mn fp16, all [B,H,A,ceil(S/11)]."""
+    if x.ndim != 4 or x.dtype != np.float16:
+        raise RuntimeError("input must be a 4D float16 array")
+    B, H, A, S = x.shape
+    nw = (S + 10) // 11
+    code = np.empty((B, H, A, nw), np.int32)
+    scale = np.empty((B, H, A, nw), np.float16)
+    mn = np.empty_like(scale)
+    x = np.ascontiguousarray(x)
+    _check(lib().orc_quant_ragged3_f16(_p(x), ctypes.c_int64(B * H * A), ctypes.c_int64(S), _p(code), _p(scale), _p(mn),
+                                       int(bool(scale_by_division))))
+    return code, scale, mn
+
+
 def quantized_gemm(group_size, fA, qB, scales, zeros, bits):
     """quantized_gemm (quant_cuda/csrc/dequantization_gemv_cuda.cu:127-248), M = 1."""
     if fA.ndim != 4 or qB.ndim != 4:

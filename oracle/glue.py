@@ -12,7 +12,7 @@ outside the path and are not restated: K, V and q enter already rotated.
 """
 import numpy as np
 
-from . import decode_attention, features_per_int, quantize_pack_last_dim
+from . import decode_attention, features_per_int, quantize_pack_last_dim, quantize_ragged3
 
 
 def split_point(cur_len, group, ratio=None, residual_length=None):
@@ -29,8 +29,11 @@ class RefLayerCache:
     def __init__(self, k_bits, v_bits, group_size, k_residual_ratio=None, v_residual_ratio=None,
                  residual_length=None):
         self.k_bits, self.v_bits = k_bits, v_bits
-        self.v_group = group_size
+        self.v_group = group_size                                  # values are quantized group_size tokens at a time
         self.k_group = 11 if k_bits == 3 else group_size          # modeling_llama_KVmix.py:49-52
+        # channel groups of the values.  3-bit values are an extension upstream does not have (its 3-bit rule needs
+        # head_dim % 11 == 0, quantization_cuda.cu:433-434): groups of 11 channels with a short last group
+        self.v_cgroup = 11 if v_bits == 3 else group_size
         self.rk, self.rv, self.window = k_residual_ratio, v_residual_ratio, residual_length
         self.kcode = self.kscale = self.kmn = None
         self.vcode = self.vscale = self.vmn = None
@@ -50,7 +53,10 @@ class RefLayerCache:
         if nv > 0:                                                   # :152-167 / :240-248
             to_q = np.ascontiguousarray(self.vfull[:, :, :nv, :])
             self.vfull = np.ascontiguousarray(self.vfull[:, :, nv:, :])
-            c, s, m = quantize_pack_last_dim(to_q, self.v_group, self.v_bits)
+            if self.v_bits == 3 and to_q.shape[3] % 11:
+                c, s, m = quantize_ragged3(to_q)
+            else:
+                c, s, m = quantize_pack_last_dim(to_q, self.v_cgroup, self.v_bits)
             cat = lambda a, b: b if a is None else np.concatenate([a, b], axis=2)
             self.vcode, self.vscale, self.vmn = cat(self.vcode, c), cat(self.vscale, s), cat(self.vmn, m)
 
@@ -72,7 +78,7 @@ class RefLayerCache:
     def attend(self, q, ref_rounding=True, attention_mask=None):
         """q: [B, nh, 1, D] fp16 -> [B, nh, 1, D] fp16 (:170-211); attention_mask as upstream's (:188-193)."""
         return decode_attention(q, self.kcode, self.kscale, self.kmn, self.kfull, self.vcode, self.vscale,
-                                self.vmn, self.vfull, self.k_bits, self.k_group, self.v_bits, self.v_group,
+                                self.vmn, self.vfull, self.k_bits, self.k_group, self.v_bits, self.v_cgroup,
                                 ref_rounding, attention_mask=attention_mask)
 
     def decode_step(self, q, k_new, v_new, ref_rounding=True, attention_mask=None):

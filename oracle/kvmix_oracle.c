@@ -168,6 +168,46 @@ int orc_quant_lastdim_f32(const float *x, int64_t rows, int64_t S, int G, int bi
 }
 
 /*
+ * EXTENSION -- no upstream counterpart, so nothing pins it ("parity unpinned"): 3-bit quantization of rows whose
+ * length S is not a multiple of 11.  Upstream rejects such rows (quantization_cuda.cu:649, and :433-434 for the
+ * value form), which rules out 3-bit values at head_dim 128.  The rule here is upstream's 3-bit group rule
+ * (:553-596, word packing :612-626) applied to groups of 11 with a last group of S % 11 elements: every group is one
+ * word; min/max, scale = (max-min)/7 and codes over the elements the group has; element 10 of a full group keeps
+ * upstream's 2-bit field (clamped at 3, :579); unused fields of the last word are 0.
+ *   code [rows, ceil(S/11)] int32, scale/mn [rows, ceil(S/11)] fp16; stored scale as in quant_lastdim_f16.
+ */
+int orc_quant_ragged3_f16(const h16 *x, int64_t rows, int64_t S, int32_t *code, h16 *scale, h16 *mn,
+                          int scale_by_division) {
+    if (S <= 0) return -4;
+    const int64_t nw = (S + 10) / 11;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        for (int64_t w = 0; w < nw; ++w) {
+            const int n = (int)((S - w * 11) < 11 ? (S - w * 11) : 11);
+            float v[11], lo = FLT_MAX, hi = -FLT_MAX;
+            for (int i = 0; i < n; ++i) {
+                v[i] = h2f(x[r * S + w * 11 + i]);
+                lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]);
+            }
+            const float sc = (hi - lo) / 7.0f;
+            uint32_t word = 0;
+            for (int i = 0; i < n; ++i) {
+                const float nrm = (v[i] - lo) / sc;
+                int q = isnan(nrm) ? 0 : (int)roundf(nrm);
+                const int emax = i >= 10 ? 3 : 7;
+                if (q > emax) q = emax;
+                if (q < 0) q = 0;
+                word |= (uint32_t)q << (i < 10 ? 3 * i : 30);
+            }
+            code[r * nw + w] = (int32_t)word;
+            scale[r * nw + w] = scale_by_division ? f2h((hi - lo) / 7.0f) : f2h((hi - lo) * (1.0f / 7.0f));
+            mn[r * nw + w] = f2h(lo);
+        }
+    }
+    return 0;
+}
+
+/*
  * quantized_gemm + execute_quantized_matvec, quant_cuda/csrc/dequantization_gemv_cuda.cu:7-124
  * (kernel) and :127-248 (shape algebra), for M = 1 (the kernel never reads blockIdx.z, so only
  * M = 1 is meaningful).
@@ -336,10 +376,12 @@ int orc_decode_attn(const h16 *q, const int32_t *kcode, const h16 *kscale, const
                     h16 *out) {
     if (Tkq + Rk != Tvq + Rv) return -9;
     if (nh % nh_kv) return -6;
-    if (vbits == 3 && D % 11) return -3;     /* quantization_cuda.cu:433-434: upstream cannot hold such V */
+    if (vbits == 3 && Gv != 11) return -2;
+    /* vbits == 3 with D % 11 != 0 is the extension format of orc_quant_ragged3_f16 (upstream cannot hold such V,
+     * quantization_cuda.cu:433-434): ceil(D/11) words and groups per token, the last one short */
     const int64_t T = Tkq + Rk, rep = nh / nh_kv;
     const int fk = orc_features_per_int(kbits), fv = orc_features_per_int(vbits);
-    const int64_t kw = Tkq / fk, kg = Tkq ? Tkq / Gk : 0, vw = D / fv, vg = D / Gv;
+    const int64_t kw = Tkq / fk, kg = Tkq ? Tkq / Gk : 0, vw = (D + fv - 1) / fv, vg = (D + Gv - 1) / Gv;
 #pragma omp parallel
     {
         float *sc = (float *)malloc(sizeof(float) * (size_t)(T + 1));
@@ -395,7 +437,7 @@ int orc_decode_attn(const h16 *q, const int32_t *kcode, const h16 *kscale, const
                     uint32_t v = (uint32_t)cw[w];
                     const int64_t g = (w * fv) / Gv;
                     const float scl = h2f(sp[g]), ze = h2f(zp[g]);
-                    for (int e = 0; e < fv; ++e) {
+                    for (int e = 0; e < fv && w * fv + e < D; ++e) {
                         int nb = (vbits == 3) ? (e < 10 ? 3 : 2) : vbits;
                         float c = (float)(v & ((1u << nb) - 1u)); v >>= nb;
                         acc_q[w * fv + e] = fmaf(fmaf(scl, c, ze), p, acc_q[w * fv + e]);
