@@ -192,6 +192,8 @@ def upstream_gpu_leg(cfg, dev, steps_per_setting=34):
     from kvmix_b200 import configs
     from kvmix_b200.cache import kv_bytes_per_head
     kinds = sorted({(q["k_bits"], q["v_bits"]) for q in cfg.quant_bits.values()})
+    if any(vb == 3 and cfg.head_dim % 11 for _, vb in kinds):
+        return {"unavailable": "upstream cannot represent 3-bit values at this head_dim (quantization_cuda.cu:433-434)"}
     B, nh, hkv, D, T = cfg.batch, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.context
     if B * hkv * D * T >= 2 ** 31:
         return {"unavailable": "batch slice would exceed upstream's 32-bit index arithmetic"}
@@ -362,6 +364,9 @@ def main():
     ap.add_argument("--context", type=int, default=None, help="override the context length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-upstream-gpu", action="store_true")
+    ap.add_argument("--v3", action="store_true",
+                    help="config 3 with its 12 K3/V3 layers as written, through the 3-bit-value extension (upstream cannot "
+                         "represent 3-bit values at head_dim 128); default: those layers run K3/V4, the map upstream could run")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="config 5 on several GPUs: attention outputs exchanged by peer stores from the attention kernel "
                          "(default; falls back to NCCL when symmetric memory is unavailable) or by an NCCL all-gather per layer")
@@ -383,7 +388,7 @@ def main():
                                   "inside the config-2 reference step"}))
             return
         return run_config4(args)
-    cfg = {2: configs.config2, 3: configs.config3, 5: configs.config5}[args.config]()
+    cfg = configs.config3(v3_as_v4=not args.v3) if args.config == 3 else {2: configs.config2, 5: configs.config5}[args.config]()
     if args.batch:
         cfg.batch = args.batch
     if args.context:

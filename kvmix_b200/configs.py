@@ -56,9 +56,11 @@ def config2():
 
 
 def config3(v3_as_v4=True):
-    # upstream cannot hold 3-bit values for head_dim 128 (128 % 11 != 0); those layers run V4
+    # upstream cannot hold 3-bit values for head_dim 128 (128 % 11 != 0): by default those layers run V4 (the map
+    # upstream could run); v3_as_v4=False runs them with the 3-bit-value extension of this library
     qb = seeded_bit_map(32, [(4, 4, 4), (12, 3, 4 if v3_as_v4 else 3), (12, 2, 2), (4, 2, 1)])
-    return HotPathConfig("cfg3-mistral-7b-b8-ctx32768-g64-w128", 32, 32, 8, 128, 64, 128, 8, 32768, 128, qb)
+    name = "cfg3-mistral-7b-b8-ctx32768-g64-w128" + ("" if v3_as_v4 else "-v3ext")
+    return HotPathConfig(name, 32, 32, 8, 128, 64, 128, 8, 32768, 128, qb)
 
 
 def config5():

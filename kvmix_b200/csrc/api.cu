@@ -14,7 +14,7 @@ int record_cuda_error(cudaError_t e) {
 }
 }  // namespace kvq
 
-extern "C" int kvq_version(void) { return 105; }   // 105: fused decode step, device-resident state, head-sharded exchange, kvq_prefill, kvq_attn_plan
+extern "C" int kvq_version(void) { return 106; }   // 105: fused decode step, device-resident state, head-sharded exchange, kvq_prefill, kvq_attn_plan; 106: 3-bit values (ragged_tail)
 
 extern "C" int kvq_features_per_int(int bits) { return (bits >= 1 && bits <= 4) ? kvq::fields_per_word(bits) : 0; }
 

@@ -61,19 +61,29 @@ __global__ void __launch_bounds__(256) quant_contig_kernel(const T *__restrict__
     const T *px = x + b * d.x_sB + h * d.x_sH + a * d.x_sA + (int64_t)u * EW;
 
     float v[EW];
+    float lo, hi;
+    bool have_range = false;
     if constexpr (sizeof(T) == 2 && (EW % 8 == 0)) {
         if (vec_ok) {
+            // min / max in fp16x2 on the raw loads (exact: the data are fp16; NaN operands are skipped as by fminf):
+            // one instruction per two elements instead of one per element
+            __half2 lo2, hi2;
 #pragma unroll
             for (int j = 0; j < EW / 8; ++j) {
                 uint4 q = __ldg(reinterpret_cast<const uint4 *>(px) + j);
                 const __half2 *hp = reinterpret_cast<const __half2 *>(&q);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
+                    if (j == 0 && k == 0) { lo2 = hp[0]; hi2 = hp[0]; }
+                    else { lo2 = __hmin2(lo2, hp[k]); hi2 = __hmax2(hi2, hp[k]); }
                     float2 f = __half22float2(hp[k]);
                     v[j * 8 + 2 * k] = f.x;
                     v[j * 8 + 2 * k + 1] = f.y;
                 }
             }
+            lo = fminf(__low2float(lo2), __high2float(lo2));
+            hi = fmaxf(__low2float(hi2), __high2float(hi2));
+            have_range = true;
         } else {
 #pragma unroll
             for (int i = 0; i < EW; ++i) v[i] = to_f32<T>(px[i]);
@@ -82,9 +92,12 @@ __global__ void __launch_bounds__(256) quant_contig_kernel(const T *__restrict__
 #pragma unroll
         for (int i = 0; i < EW; ++i) v[i] = to_f32<T>(px[i]);
     }
-    float lo = v[0], hi = v[0];
+    if (!have_range) {
+        lo = v[0];
+        hi = v[0];
 #pragma unroll
-    for (int i = 1; i < EW; ++i) { lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]); }
+        for (int i = 1; i < EW; ++i) { lo = fminf(lo, v[i]); hi = fmaxf(hi, v[i]); }
+    }
     for (int o = 1; o < tpg; o <<= 1) {
         lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
         hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));

@@ -64,10 +64,11 @@ def load_profile_model(upstream_root):
     return mod.profile_model
 
 
-def check_quant_bits(quant_bits, n_layers, head_dim=128):
+def check_quant_bits(quant_bits, n_layers, head_dim=128, allow_v3_extension=False):
     """Validate a profiler bit map for ``n_layers`` layers; returns it with integer layer keys in order.
     3-bit values are refused for the reason upstream's own quantizer refuses them: its 3-bit format packs groups of 11
-    and head_dim % 11 != 0 (quant_cuda/csrc/quantization_cuda.cu:637-639, 649)."""
+    and head_dim % 11 != 0 (quant_cuda/csrc/quantization_cuda.cu:637-639, 649) -- unless ``allow_v3_extension`` opts
+    into this library's own layout for them (12 words per token, a short last group), which upstream cannot read."""
     out = {}
     for layer in range(n_layers):
         e = quant_bits.get(layer, quant_bits.get(str(layer)))
@@ -79,7 +80,7 @@ def check_quant_bits(quant_bits, n_layers, head_dim=128):
         kb, vb = int(e["k_bits"]), int(e["v_bits"])
         if kb not in (1, 2, 3, 4) or vb not in (1, 2, 3, 4):
             raise ValueError(f"layer {layer}: Supported quantization bits: 1, 2, 3, 4")
-        if vb == 3 and head_dim % 11 != 0:
+        if vb == 3 and head_dim % 11 != 0 and not allow_v3_extension:
             raise ValueError(f"layer {layer}: 3-bit values need head_dim % 11 == 0 (upstream's 3-bit format packs groups of 11)")
         rk, rv = float(e["k_residual_ratio"]), float(e["v_residual_ratio"])
         if not (0.0 <= rk < 1.0 and 0.0 <= rv < 1.0):
@@ -95,12 +96,12 @@ def default_entry(k_bits, v_bits):
 
 
 def caches_from_profile(quant_bits, batch, kv_heads, head_dim, max_tokens, group_size, device="cuda",
-                        residual_length=None):
+                        residual_length=None, allow_v3_extension=False):
     """One ``KVmixLayerCache`` per layer of the (checked) bit map.  Upstream's window policy -- keep
     ``int(ratio * current_fp16_len)`` tokens in fp16, with the ratio the profiler chose per layer -- is the default; a
     fixed ``residual_length`` replaces it when given."""
     from .cache import KVmixLayerCache
-    qb = check_quant_bits(quant_bits, len(quant_bits), head_dim)
+    qb = check_quant_bits(quant_bits, len(quant_bits), head_dim, allow_v3_extension)
     caches = []
     for layer in range(len(qb)):
         e = qb[layer]

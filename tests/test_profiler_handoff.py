@@ -52,6 +52,7 @@ def test_bit_map_checks():
     bad[2] = dict(good[2], v_bits=3)
     with pytest.raises(ValueError, match="3-bit values"):
         profiler.check_quant_bits(bad, 4)
+    assert profiler.check_quant_bits(bad, 4, allow_v3_extension=True)[2]["v_bits"] == 3
     bad[2] = dict(good[2], k_bits=5)
     with pytest.raises(ValueError, match="Supported quantization bits"):
         profiler.check_quant_bits(bad, 4)
