@@ -364,6 +364,10 @@ def main():
     ap.add_argument("--context", type=int, default=None, help="override the context length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-upstream-gpu", action="store_true")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="device-resident leg: replay the whole decode step (every layer's fused launch, and the exchange waits "
+                         "of a head-sharded run) from one CUDA graph with the cache lengths held on the device; auto = when "
+                         "every layer's geometry is fused by the library, else launch layer by layer from the host")
     ap.add_argument("--v3", action="store_true",
                     help="config 3 with its 12 K3/V3 layers as written, through the 3-bit-value extension (upstream cannot "
                          "represent 3-bit values at head_dim 128); default: those layers run K3/V4, the map upstream could run")
@@ -420,7 +424,8 @@ def main():
         b_lo, b_hi = sharding.shard_batch(cfg.batch, world, rank)
         B, nh, hkv = b_hi - b_lo, cfg.n_heads, cfg.n_kv_heads
 
-    caches = configs.build_layer_caches(cfg, B, dev, extra_tokens=3 * (W + K) + 8, kv_heads=hkv, seed=rank)
+    caches = configs.build_layer_caches(cfg, B, dev, extra_tokens=3 * (W + K) + 24, kv_heads=hkv, seed=rank,
+                                        device_state=args.graph != "off")
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     mk = lambda h: torch.randn((B, h, 1, D), generator=g, device=dev, dtype=torch.float16)
     dq, dk, dv = [mk(nh) for _ in range(L)], [mk(hkv) for _ in range(L)], [mk(hkv) for _ in range(L)]
@@ -521,22 +526,54 @@ def main():
         return float(ms.item())
 
     # device-resident run -------------------------------------------------------------------------
-    for _ in range(W):
+    for _ in range(W - 1):
         step_device(False)
+    step_device(True)                      # the last warm-up step, launch by launch with CUDA events around each layer
+    torch.cuda.synchronize()
+    eager_events, attn_events = attn_events, []
+    captured = None
+    if args.graph != "off":
+        ok = all(c._fused is True and c.steady() for c in caches)
+        if world > 1:
+            flag = torch.tensor([int(ok)], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = bool(flag.item())
+        if ok:
+            from kvmix_b200 import CapturedDecodeStep
+            captured = CapturedDecodeStep(caches, dq, dk, dv, dout, max_replays=K + 3, peers=peer)
+            for _ in range(3):
+                captured.replay()
+        elif args.graph == "on":
+            raise SystemExit("--graph on: a layer of this configuration is not served by the fused decode step")
+        else:
+            for c in caches:               # host-driven from here on: the host mirror is authoritative
+                c.state = None
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches0 = ops.LAUNCHES[0]
+    step_bytes0 = sum(c.packed_bytes() + 2 * B * nh * D * 2 for c in caches)
     torch.cuda.profiler.start()            # `ncu --profile-from-start off` then lists the timed region only
-    ms_total = timed(lambda: step_device(True), K)
+    if captured is not None:
+        ms_total = timed(lambda: captured.replay(), K)
+    else:
+        ms_total = timed(lambda: step_device(True), K)
     torch.cuda.profiler.stop()
     launches = ops.LAUNCHES[0] - launches0
     clocks = sampler.stop() if rank == 0 else None
-    attn_ms = sum(e0.elapsed_time(e1) for e0, e1, _, _ in attn_events)
-    attn_bytes = sum(b for _, _, b, _ in attn_events)
-    n_attn = len(attn_events)
+    step_bytes1 = sum(c.packed_bytes() + 2 * B * nh * D * 2 for c in caches)
+    if captured is not None:
+        # no events inside a graph: the launch duration is the whole timed region over its launches (gaps included)
+        launches = K * L * (2 if peer is not None else 1)
+        attn_ms, attn_bytes, n_attn = ms_total, (step_bytes0 + step_bytes1) / 2 * K, K * L
+        src_events = eager_events
+    else:
+        attn_ms = sum(e0.elapsed_time(e1) for e0, e1, _, _ in attn_events)
+        attn_bytes = sum(b for _, _, b, _ in attn_events)
+        n_attn = len(attn_events)
+        src_events = attn_events
     per_kind = {}
-    for e0, e1, b, kv in attn_events:
+    for e0, e1, b, kv in src_events:
         t = per_kind.setdefault(kv, [0.0, 0.0, 0])
         t[0] += e0.elapsed_time(e1)
         t[1] += b
@@ -580,6 +617,8 @@ def main():
                                   " (3-bit keys use group 11), seeded",
                        "l2_policy": "inputs larger than L2: every step streams the whole cache "
                                     f"({attn_bytes_all / max(1, n_attn) * L / 1e9:.1f} GB per step per GPU)",
+                       "step_launched_as": ("one CUDA graph per decode step (cache lengths and ring starts on the device)"
+                                            if captured is not None else "one launch per layer from the host"),
                        "parallelism": ((f"kv-head-sharded x{world}, attention outputs exchanged by peer stores from the attention "
                                         f"kernel + bounded device-side wait (NVLink, no collective launch)" if peer is not None else
                                         f"kv-head-sharded x{world}, per-layer NCCL all-gather of the attention output")
@@ -593,9 +632,13 @@ def main():
                          "bytes_per_launch": attn_bytes_all / max(1, n_attn),
                          "us_per_launch": attn_ms_all * 1e3 / max(1, n_attn), "launches_timed": n_attn,
                          "timed_launch_is": "one decode step of one layer: ring append + (when due) group quantization + attention",
+                         "launch_timing": ("CUDA events around the K replays of the step graph, divided by its attention launches "
+                                           "(no events inside a graph: gaps and exchange waits are included); per_bit_setting "
+                                           "comes from the last warm-up step, launched layer by layer with events"
+                                           if captured is not None else "CUDA events around every launch of the timed region"),
                          "per_bit_setting": {f"K{kb}V{vb}": {"us": t[0] * 1e3 / t[2], "GBs": t[1] / (t[0] * 1e-3) / 1e9}
                                              for (kb, vb), t in sorted(per_kind.items())},
-                         "attention_share_of_step": attn_ms_all / ms_total},
+                         "attention_share_of_step": None if captured is not None else attn_ms_all / ms_total},
             "e2e": {"value": cfg.batch * K / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / K,
                     "h2d_bytes_per_step": world * L * B * (nh + 2 * hkv) * D * 2,
                     "d2h_bytes_per_step": world * L * B * nh * D * 2,

@@ -377,6 +377,14 @@ typedef struct {
  * died, a shard that was never launched).  status must be device memory holding two int32, zeroed by the caller.
  */
 int kvq_peer_wait(const uint32_t *counter, uint32_t expected, uint32_t max_polls, int32_t *status, kvq_stream_t stream);
+/*
+ * The same bounded wait with the target kept on the device, for steps replayed from a CUDA graph: *generation (device
+ * memory, one uint32 per counter, zeroed by the caller together with the counter) is incremented by the kernel, and
+ * the wait is for generation * per_use arrivals, per_use being what one use of the counter adds (batch * all ranks'
+ * query heads).  No argument changes from step to step.  No upstream counterpart.
+ */
+int kvq_peer_wait_next(const uint32_t *counter, uint32_t per_use, uint32_t *generation, uint32_t max_polls,
+                       int32_t *status, kvq_stream_t stream);
 
 uint64_t kvq_decode_attn_workspace_bytes(int32_t B, int32_t nh, int32_t T);
 /* Clears the counters of a workspace for B * nh query heads (asynchronously, on `stream`). */

@@ -5,8 +5,9 @@ calling an operator needs the built library and CUDA tensors -- there is no CPU 
 """
 from .ops import (decode_attention, features_per_int, process_key_quantization_cuda,  # noqa: F401
                   process_value_quantization_cuda, quantize_into, quantize_pack_last_dim_cuda, quantized_gemm)
-from .cache import KVmixLayerCache, KVmixPast, attention_step, kv_bytes_per_head, split_point  # noqa: F401
+from .cache import (CapturedDecodeStep, KVmixLayerCache, KVmixPast, attention_step, kv_bytes_per_head,  # noqa: F401
+                    split_point)
 
 __all__ = ["quantize_pack_last_dim_cuda", "quantized_gemm", "process_key_quantization_cuda",
-           "process_value_quantization_cuda", "decode_attention", "quantize_into", "KVmixLayerCache",
+           "process_value_quantization_cuda", "decode_attention", "quantize_into", "KVmixLayerCache", "CapturedDecodeStep",
            "attention_step", "KVmixPast", "kv_bytes_per_head", "split_point", "features_per_int"]

@@ -126,6 +126,8 @@ def lib():
         L.kvq_decode_attn_plan.argtypes = [C.POINTER(AttnArgs), i32, C.POINTER(AttnPlan)]
         L.kvq_peer_wait.restype = C.c_int
         L.kvq_peer_wait.argtypes = [vp, C.c_uint32, C.c_uint32, vp, vp]
+        L.kvq_peer_wait_next.restype = C.c_int
+        L.kvq_peer_wait_next.argtypes = [vp, C.c_uint32, vp, C.c_uint32, vp, vp]
         L.kvq_prefill.restype = C.c_int
         L.kvq_prefill.argtypes = [C.POINTER(PrefillArgs), vp]
         L.kvq_decode_attn_workspace_init.restype = C.c_int
@@ -138,7 +140,7 @@ def lib():
 
 EXPORTS = ["kvq_version", "kvq_error_string", "kvq_last_cuda_error", "kvq_features_per_int",
            "kvq_quant_lastdim", "kvq_append_kv", "kvq_gemv", "kvq_decode_attn", "kvq_decode_attn_workspace_bytes",
-           "kvq_decode_attn_static", "kvq_decode_attn_plan", "kvq_decode_attn_workspace_init", "kvq_prefill", "kvq_peer_wait", "kvq_append_k", "kvq_append_v"]
+           "kvq_decode_attn_static", "kvq_decode_attn_plan", "kvq_decode_attn_workspace_init", "kvq_prefill", "kvq_peer_wait", "kvq_peer_wait_next", "kvq_append_k", "kvq_append_v"]
 
 
 def check(rc):

@@ -441,6 +441,60 @@ def kv_bytes_per_head(tkq, tvq, rk, rv, D, k_bits, k_group, v_bits, v_group):
     return kcodes + ksz + vcodes + vsz + resid
 
 
+class CapturedDecodeStep:
+    """One decode step of a stack of layer caches -- every layer's fused launch and, for head-sharded caches, its
+    exchange wait -- captured once in a CUDA graph and replayed for the following tokens with no host work per layer.
+
+    The caches must hold their state on the device (``device_state=True``), be in steady state (``steady()``) and have
+    a geometry the library fuses.  ``q``, ``k_new``, ``v_new``, ``out`` are per-layer lists of static tensors: write
+    the next token's inputs into them, call ``replay()``, read ``out`` (or, head-sharded, ``gathered``).  The grids are
+    laid out for ``max_replays`` further tokens; replaying more often than that raises.  Upstream has no counterpart
+    (its forward decides on the host, per layer and step, how many tokens to quantize: modeling_llama_KVmix.py:115-126).
+    """
+
+    def __init__(self, caches, q, k_new, v_new, out, max_replays, peers=None):
+        if not caches or any(c.state is None for c in caches):
+            raise RuntimeError("a captured decode step needs caches made with device_state=True")
+        if any(not c.steady() for c in caches):
+            raise RuntimeError("a captured decode step needs caches in steady state (at most one group due per step)")
+        self.caches, self.left, self.peers = list(caches), int(max_replays), peers
+        self.gathered = [None] * len(caches)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        for c, ql in zip(caches, q):                            # nothing may be allocated while capturing
+            c._workspace(ql.shape[1], side.cuda_stream, ql.device)
+        torch.cuda.synchronize()
+        mirrors = [(c.kv_seq_len, c.tkq, c.tvq, c.k_start, c.v_start, c.k_len, c.v_len) for c in caches]
+        layer0 = peers.layer if peers is not None else 0
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(self.graph, stream=side):
+                for l, c in enumerate(caches):
+                    r = c.decode_step(q[l], k_new[l], v_new[l], out=out[l], peers=peers,
+                                      plan_tokens=c.kv_seq_len + self.left)
+                    if r is None or c._fused is not True:
+                        raise RuntimeError(f"layer {l}: the library does not fuse this geometry")
+                    if peers is not None:
+                        self.gathered[l] = peers.wait()
+        torch.cuda.current_stream().wait_stream(side)
+        # capturing launched nothing: put the host mirrors (and the exchange's layer counter) back
+        for c, m in zip(caches, mirrors):
+            c.kv_seq_len, c.tkq, c.tvq, c.k_start, c.v_start, c.k_len, c.v_len = m
+        if peers is not None:
+            if (peers.layer - layer0) % peers.depth:
+                raise RuntimeError("the layers of a step must use the exchange buffers a whole number of rounds")
+            peers.layer = layer0
+
+    def replay(self, steps=1):
+        if steps > self.left:
+            raise RuntimeError("captured decode step replayed beyond the context it was laid out for")
+        for _ in range(steps):
+            self.graph.replay()
+        self.left -= steps
+        for c in self.caches:
+            c.advance_mirror(steps)
+
+
 class KVmixPast(tuple):
     """Upstream's past_key_value 9-tuple backed by a preallocated KVmixLayerCache (``.cache``): element [8] is
     kv_seq_len as upstream reads it, elements [0..7] are lazily built views for whoever indexes them.

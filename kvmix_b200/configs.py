@@ -81,7 +81,8 @@ def synth_kv(batch, kv_heads, tokens, head_dim, device, seed, outliers=4, outlie
     return k, v
 
 
-def build_layer_caches(cfg, batch, device, extra_tokens, kv_heads=None, seed=0, use_ratio_policy=False):
+def build_layer_caches(cfg, batch, device, extra_tokens, kv_heads=None, seed=0, use_ratio_policy=False,
+                       device_state=False):
     """One prefilled KVmixLayerCache per layer, holding ``cfg.context`` synthetic tokens."""
     from .cache import KVmixLayerCache
     kv_heads = kv_heads or cfg.n_kv_heads
@@ -91,7 +92,7 @@ def build_layer_caches(cfg, batch, device, extra_tokens, kv_heads=None, seed=0, 
         pol = (dict(k_residual_ratio=qb["k_residual_ratio"], v_residual_ratio=qb["v_residual_ratio"])
                if use_ratio_policy else dict(residual_length=cfg.residual_length))
         c = KVmixLayerCache(batch, kv_heads, cfg.head_dim, cfg.context + extra_tokens, qb["k_bits"], qb["v_bits"],
-                            cfg.group_size, device=device, **pol)
+                            cfg.group_size, device=device, device_state=device_state, **pol)
         k, v = synth_kv(batch, kv_heads, cfg.context, cfg.head_dim, device, seed * 1000 + layer)
         c.prefill(k, v)
         del k, v

@@ -57,7 +57,32 @@ __global__ void peer_wait_kernel(const uint32_t *counter, uint32_t expected, uin
     status[0] = 1;                                             // gave up: the host reads this after the step
     status[1] = (int32_t)seen;
 }
+// The same wait with the arrival target kept on the device: generation g of this counter (incremented here) waits for
+// g * per_use arrivals, so the launch carries no per-step argument and replays from a CUDA graph.
+__global__ void peer_wait_next_kernel(const uint32_t *counter, uint32_t per_use, uint32_t *generation, uint32_t max_polls,
+                                      int32_t *status) {
+    const uint32_t g = *generation + 1u;
+    *generation = g;
+    const uint32_t expected = g * per_use;
+    uint32_t seen = 0;
+    for (uint32_t i = 0; i < max_polls; ++i) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+        if ((int32_t)(seen - expected) >= 0) return;
+        __nanosleep(1000);
+    }
+    status[0] = 1;
+    status[1] = (int32_t)seen;
+}
 }  // namespace kvq
+
+extern "C" int kvq_peer_wait_next(const uint32_t *counter, uint32_t per_use, uint32_t *generation, uint32_t max_polls,
+                                  int32_t *status, kvq_stream_t stream) {
+    using namespace kvq;
+    if (!counter || !status || !generation) return KVQ_ERR_NULL;
+    if (max_polls == 0 || per_use == 0) return KVQ_ERR_SHAPE;
+    peer_wait_next_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(counter, per_use, generation, max_polls, status);
+    return check_launch();
+}
 
 extern "C" int kvq_peer_wait(const uint32_t *counter, uint32_t expected, uint32_t max_polls, int32_t *status,
                              kvq_stream_t stream) {

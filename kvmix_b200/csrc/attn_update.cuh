@@ -168,11 +168,14 @@ __device__ __forceinline__ void dev_state_commit(const kvq_attn_args &b, int tid
 // at local head h0 of sequence b) go to every rank's gather buffer, then every rank's arrival counter is raised by
 // n_heads.  Every thread of the CTA calls it (CTA barrier inside).  Plain peer stores and one system-scope
 // fence + atomic per rank: no multicast, nothing waits here.
-__device__ __forceinline__ void peer_publish(const kvq_attn_args &a, int b, int h0, int n_heads, const __half *vals, int tid) {
+template <int N>
+__device__ __forceinline__ void peer_publish(const kvq_attn_args &a, int b, int h0, int n_heads, const __half (&vals)[N], int tid) {
     if (a.n_peers <= 0) return;
     for (int p = 0; p < a.n_peers; ++p) {
         __half *dst = static_cast<__half *>(a.peer_out[p]) + (int64_t)b * a.peer_sB + (int64_t)(a.peer_head0 + h0) * a.peer_sH + tid;
-        for (int i = 0; i < n_heads; ++i) dst[(int64_t)i * a.peer_sH] = vals[i];
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+            if (i < n_heads) dst[(int64_t)i * a.peer_sH] = vals[i];
     }
     __syncthreads();                                           // every thread's stores are issued ...
     if (tid < a.n_peers) {

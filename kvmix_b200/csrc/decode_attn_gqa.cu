@@ -534,7 +534,7 @@ __device__ __forceinline__ void gqa_pv_packed(const kvq_attn_args &a, const int3
 // ---------------------------------------------------------------------------------------------
 // One segment: tokens [t0, t1) of head group s (sequence b, kv head hk, quad of query heads); segment `seg` of `cnt`.
 template <int KB, int VB>
-__device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, int n_scores, int qhv, int s, int t0, int t1, int seg,
+__device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, const kvq_attn_args &ac, int n_scores, int qhv, int s, int t0, int t1, int seg,
                                             int cnt, int n_whole, float *__restrict__ parts,
                                             unsigned int *__restrict__ counters) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -689,18 +689,24 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, int n_scores
     }
     __half res[kQH];
     if (cnt == 1) {
-        for (int hs = 0; hs < qhv; ++hs) {
-            __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)(h_first + hs) * a.o_sH;
-            res[hs] = __float2half_rn(o[hs] / sm.misc[4 + hs]);
-            out[tid] = res[hs];
+#pragma unroll
+        for (int hs = 0; hs < kQH; ++hs) {
+            if (hs < qhv) {
+                __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)(h_first + hs) * a.o_sH;
+                res[hs] = __float2half_rn(o[hs] / sm.misc[4 + hs]);
+                out[tid] = res[hs];
+            }
         }
-        peer_publish(a, b, h_first, qhv, res, tid);
+        peer_publish(ac, b, h_first, qhv, res, tid);
         return;
     }
     float *part = parts + ((int64_t)(s - n_whole) * cnt + seg) * qhv * kPart;    // partials of the cut head groups only
-    for (int hs = 0; hs < qhv; ++hs) {
-        part[hs * kPart + tid] = o[hs];
-        if (tid == 0) { part[hs * kPart + kHeadDim] = sm.misc[hs]; part[hs * kPart + kHeadDim + 1] = sm.misc[4 + hs]; }
+#pragma unroll
+    for (int hs = 0; hs < kQH; ++hs) {
+        if (hs < qhv) {
+            part[hs * kPart + tid] = o[hs];
+            if (tid == 0) { part[hs * kPart + kHeadDim] = sm.misc[hs]; part[hs * kPart + kHeadDim + 1] = sm.misc[4 + hs]; }
+        }
     }
     __syncthreads();
     if (tid == 0) {
@@ -710,23 +716,79 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, int n_scores
     }
     __syncthreads();
     if (sm.misc[8] == 0.f) return;
+    // The last CTA merges the cnt segments of its head group.  A long context over few heads means hundreds of segments,
+    // so the merge keeps many loads in flight instead of walking the segments one dependent round trip at a time:
+    // the maxima first (thread t looks at segments t, t + 128, ...), then warp w sums segments w, w + 4, ... with lane
+    // l owning channels 2l, 2l + 1, 64 + 2l, 65 + 2l of every head; the four warps' sums meet in shared memory in warp
+    // order.  The mapping is fixed, so results are run-to-run identical.
     const float *base = parts + (int64_t)(s - n_whole) * cnt * qhv * kPart;
-    for (int hs = 0; hs < qhv; ++hs) {
-        const float *bh = base + hs * kPart;
-        float M = kMaskFloor;
-        for (int i = 0; i < cnt; ++i) M = fmaxf(M, __ldcg(bh + i * qhv * kPart + kHeadDim));
-        float L = 0.f, acc = 0.f;
-        for (int i = 0; i < cnt; ++i) {
-            const float w = __expf(__ldcg(bh + i * qhv * kPart + kHeadDim) - M);
-            L = fmaf(__ldcg(bh + i * qhv * kPart + kHeadDim + 1), w, L);
-            acc = fmaf(__ldcg(bh + i * qhv * kPart + tid), w, acc);
+    const int stride = qhv * kPart;
+    float M[kQH];
+#pragma unroll
+    for (int hs = 0; hs < kQH; ++hs) M[hs] = kMaskFloor;
+    for (int i = tid; i < cnt; i += kMmaThreads) {
+#pragma unroll
+        for (int hs = 0; hs < kQH; ++hs)
+            if (hs < qhv) M[hs] = fmaxf(M[hs], __ldcg(base + (int64_t)i * stride + hs * kPart + kHeadDim));
+    }
+#pragma unroll
+    for (int hs = 0; hs < kQH; ++hs) {
+        M[hs] = warp_max(M[hs]);
+        if (lane == 0) sm.misc[16 + warp * kQH + hs] = M[hs];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int hs = 0; hs < kQH; ++hs) {
+        M[hs] = sm.misc[16 + hs];
+#pragma unroll
+        for (int w = 1; w < kMmaWarps; ++w) M[hs] = fmaxf(M[hs], sm.misc[16 + w * kQH + hs]);
+    }
+    float2 acc0[kQH], acc1[kQH];
+    float Ls[kQH];
+#pragma unroll
+    for (int hs = 0; hs < kQH; ++hs) { acc0[hs] = make_float2(0.f, 0.f); acc1[hs] = make_float2(0.f, 0.f); Ls[hs] = 0.f; }
+#pragma unroll 2
+    for (int i = warp; i < cnt; i += kMmaWarps) {
+        const float *pi = base + (int64_t)i * stride;
+#pragma unroll
+        for (int hs = 0; hs < kQH; ++hs) {
+            if (hs < qhv) {
+                const float w = __expf(__ldcg(pi + hs * kPart + kHeadDim) - M[hs]);
+                Ls[hs] = fmaf(__ldcg(pi + hs * kPart + kHeadDim + 1), w, Ls[hs]);
+                const float2 p0 = __ldcg(reinterpret_cast<const float2 *>(pi + hs * kPart) + lane);
+                const float2 p1 = __ldcg(reinterpret_cast<const float2 *>(pi + hs * kPart + 64) + lane);
+                acc0[hs].x = fmaf(p0.x, w, acc0[hs].x); acc0[hs].y = fmaf(p0.y, w, acc0[hs].y);
+                acc1[hs].x = fmaf(p1.x, w, acc1[hs].x); acc1[hs].y = fmaf(p1.y, w, acc1[hs].y);
+            }
         }
-        __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)(h_first + hs) * a.o_sH;
-        res[hs] = __float2half_rn(acc / L);
-        out[tid] = res[hs];
+    }
+    {   // this warp's sums into its own (now idle) region: [kQH][128] floats, then kQH sums
+        float *mine = reinterpret_cast<float *>(sm.ring);
+#pragma unroll
+        for (int hs = 0; hs < kQH; ++hs) {
+            reinterpret_cast<float2 *>(mine + hs * kHeadDim)[lane] = acc0[hs];
+            reinterpret_cast<float2 *>(mine + hs * kHeadDim + 64)[lane] = acc1[hs];
+            if (lane == 0) mine[kQH * kHeadDim + hs] = Ls[hs];
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int hs = 0; hs < kQH; ++hs) {
+        if (hs < qhv) {
+            float acc = 0.f, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < kMmaWarps; ++w) {
+                const float *reg = reinterpret_cast<const float *>(after_scores + w * kRegion);
+                acc += reg[hs * kHeadDim + tid];
+                L += reg[kQH * kHeadDim + hs];
+            }
+            __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)(h_first + hs) * a.o_sH;
+            res[hs] = __float2half_rn(acc / L);
+            out[tid] = res[hs];
+        }
     }
     if (tid == 0) counters[s] = 0u;
-    peer_publish(a, b, h_first, qhv, res, tid);
+    peer_publish(ac, b, h_first, qhv, res, tid);
 }
 
 template <int KB, int VB, bool DEV>
@@ -740,11 +802,11 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_attn_gqa_kernel(const _
         dev_state_step(a, b);
         plan_cta(plan, b.T, blockIdx.x, group, t0, t1, seg, cnt);
         if (cnt > 1) cnt = min(cnt, (b.T + plan.seg_units * plan.unit - 1) / (plan.seg_units * plan.unit));
-        if (t0 < b.T) gqa_segment<KB, VB>(b, plan.n_scores, qhv, group, t0, t1, seg, cnt, plan.n_whole, parts, counters);
+        if (t0 < b.T) gqa_segment<KB, VB>(b, a, plan.n_scores, qhv, group, t0, t1, seg, cnt, plan.n_whole, parts, counters);
         dev_state_commit(b, threadIdx.x);
     } else {
         plan_cta(plan, a.T, blockIdx.x, group, t0, t1, seg, cnt);
-        gqa_segment<KB, VB>(a, plan.n_scores, qhv, group, t0, t1, seg, cnt, plan.n_whole, parts, counters);
+        gqa_segment<KB, VB>(a, a, plan.n_scores, qhv, group, t0, t1, seg, cnt, plan.n_whole, parts, counters);
     }
 }
 

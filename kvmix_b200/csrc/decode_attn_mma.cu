@@ -607,7 +607,7 @@ __device__ __forceinline__ void qk_tail_mma(const kvq_attn_args &a, const __half
 // ---------------------------------------------------------------------------------------------
 // One segment: tokens [t0, t1) of query head (b, h); segment `seg` of the `cnt` the head is cut into.
 template <int KB, int VB>
-__device__ __forceinline__ void attn_segment(const kvq_attn_args &a, int n_scores, int s, int t0, int t1, int seg,
+__device__ __forceinline__ void attn_segment(const kvq_attn_args &a, const kvq_attn_args &ac, int n_scores, int s, int t0, int t1, int seg,
                                              int cnt, int n_whole, float *__restrict__ parts,
                                              unsigned int *__restrict__ counters) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -749,9 +749,9 @@ __device__ __forceinline__ void attn_segment(const kvq_attn_args &a, int n_score
     }
     __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)h * a.o_sH;
     if (cnt == 1) {
-        const __half r = __float2half_rn(o / l);
-        out[tid] = r;
-        peer_publish(a, b, h, 1, &r, tid);
+        const __half r[1] = {__float2half_rn(o / l)};
+        out[tid] = r[0];
+        peer_publish(ac, b, h, 1, r, tid);
         return;
     }
     constexpr int kPart = kHeadDim + 2;
@@ -777,10 +777,10 @@ __device__ __forceinline__ void attn_segment(const kvq_attn_args &a, int n_score
         L = fmaf(__ldcg(base + i * kPart + kHeadDim + 1), w, L);
         acc = fmaf(__ldcg(base + i * kPart + tid), w, acc);
     }
-    const __half r = __float2half_rn(acc / L);
-    out[tid] = r;
+    const __half r[1] = {__float2half_rn(acc / L)};
+    out[tid] = r[0];
     if (tid == 0) counters[s] = 0u;                          // the head is done: its counter is ready for the next launch
-    peer_publish(a, b, h, 1, &r, tid);
+    peer_publish(ac, b, h, 1, r, tid);
 }
 
 // CTA = one segment (see attn_plan.cuh): a whole head, or one of the k pieces of a head that is cut.
@@ -797,11 +797,11 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(const _
         dev_state_step(a, b);
         plan_cta(plan, b.T, blockIdx.x, head, t0, t1, seg, cnt);
         if (cnt > 1) cnt = min(cnt, (b.T + plan.seg_units * plan.unit - 1) / (plan.seg_units * plan.unit));
-        if (t0 < b.T) attn_segment<KB, VB>(b, plan.n_scores, head, t0, t1, seg, cnt, plan.n_whole, parts, counters);
+        if (t0 < b.T) attn_segment<KB, VB>(b, a, plan.n_scores, head, t0, t1, seg, cnt, plan.n_whole, parts, counters);
         dev_state_commit(b, threadIdx.x);
     } else {
         plan_cta(plan, a.T, blockIdx.x, head, t0, t1, seg, cnt);
-        attn_segment<KB, VB>(a, plan.n_scores, head, t0, t1, seg, cnt, plan.n_whole, parts, counters);
+        attn_segment<KB, VB>(a, a, plan.n_scores, head, t0, t1, seg, cnt, plan.n_whole, parts, counters);
     }
 }
 

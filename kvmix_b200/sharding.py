@@ -114,7 +114,7 @@ class PeerGather:
         if self.world > 8:
             raise ValueError("at most 8 ranks")
         self.status = torch.zeros(2, dtype=torch.int32, device=device)
-        self.uses = [0] * depth
+        self.gen = torch.zeros(depth * 32, dtype=torch.int32, device=device)   # uses of each counter so far (device side)
         self.layer = 0
         self._slot_bytes = batch * self.world * nh_local * head_dim * 2
 
@@ -138,12 +138,13 @@ class PeerGather:
     def wait(self):
         """Enqueue the bounded wait for the layer just launched; returns the gathered [B, nh, 1, D] view."""
         slot = self.layer % self.depth
-        self.uses[slot] += 1
-        expected = (self.uses[slot] * self.B * self.world * self.nhl) & 0xFFFFFFFF
         from . import _lib
-        _lib.check(self._lib.kvq_peer_wait(self._C.c_void_p(self.cnt.data_ptr() + slot * 128), expected, self.MAX_POLLS,
-                                           self._C.c_void_p(self.status.data_ptr()),
-                                           self._C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        # the target (uses so far x arrivals per use) lives on the device, so this launch replays from a CUDA graph
+        _lib.check(self._lib.kvq_peer_wait_next(self._C.c_void_p(self.cnt.data_ptr() + slot * 128),
+                                                self.B * self.world * self.nhl,
+                                                self._C.c_void_p(self.gen.data_ptr() + slot * 128), self.MAX_POLLS,
+                                                self._C.c_void_p(self.status.data_ptr()),
+                                                self._C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         self.layer += 1
         return self.buf[slot]
 

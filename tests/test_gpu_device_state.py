@@ -74,3 +74,65 @@ def test_device_driven_steps_match_host_driven(cuda, kb, vb, G, nh, hkv, policy,
     assert (dev.kv_seq_len, dev.tkq, dev.tvq, dev.k_start, dev.v_start) == (host.kv_seq_len, host.tkq, host.tvq, host.k_start, host.v_start)
     for x, y in zip(dev.as_tuple()[:8], host.as_tuple()[:8]):
         assert torch.equal(x, y)                                 # codes, scales, minima and tails bit for bit
+
+
+@pytest.mark.parametrize("kinds,nh,hkv,G,with_exchange", [([(4, 4), (3, 2), (2, 2)], 4, 4, 32, False),
+                                                          ([(4, 4), (3, 2), (3, 2), (2, 2)], 8, 2, 128, True)])
+def test_whole_step_captured_once(cuda, kinds, nh, hkv, G, with_exchange):
+    """A stack of layers (different bit settings) as ONE captured graph, replayed 40 times, against the same stack
+    driven from the host layer by layer; with_exchange adds the head-sharded exchange of a one-rank "world" (peer
+    stores into this GPU's own gather buffer and the device-side generation wait) inside the graph."""
+    import kvmix_b200 as kv
+    from kvmix_b200 import sharding
+    B, L0, steps = 2, 900, 40
+    layers = len(kinds)
+    k, v = make_kv(5, B, hkv, L0 + steps + 2)
+    kt, vt = _t(k, cuda), _t(v, cuda)
+    mk = lambda kb, vb, ds: kv.KVmixLayerCache(B, hkv, 128, L0 + steps + 16, kb, vb, G, residual_length=128, device=cuda,
+                                               device_state=ds)
+    host = [mk(kb, vb, False) for kb, vb in kinds]
+    devc = [mk(kb, vb, True) for kb, vb in kinds]
+    for c in host + devc:
+        c.prefill(kt[:, :, :L0], vt[:, :, :L0])
+    peers = None
+    if with_exchange:
+        pair = [(torch.zeros((2, B, nh, 1, 128), dtype=torch.float16, device=cuda), torch.zeros(64, dtype=torch.int32, device=cuda))]
+        peers = sharding.PeerGather(B, nh, 128, cuda, peers=pair, rank=0)
+    qs = [torch.zeros((B, nh, 1, 128), device=cuda, dtype=torch.float16) for _ in range(layers)]
+    ks = [torch.zeros((B, hkv, 1, 128), device=cuda, dtype=torch.float16) for _ in range(layers)]
+    vs = [torch.zeros((B, hkv, 1, 128), device=cuda, dtype=torch.float16) for _ in range(layers)]
+    outs = [torch.zeros((B, nh, 1, 128), device=cuda, dtype=torch.float16) for _ in range(layers)]
+    # one eager step first: the fused path is taken and the workspaces exist
+    for l in range(layers):
+        q = _t(make_q(1000 + l, B, nh), cuda)
+        a = host[l].decode_step(q, kt[:, :, L0:L0 + 1], vt[:, :, L0:L0 + 1])
+        b = devc[l].decode_step(q, kt[:, :, L0:L0 + 1], vt[:, :, L0:L0 + 1], peers=peers)
+        if peers is not None:
+            assert torch.equal(peers.wait(), a)
+        assert torch.equal(a, b)
+    step = kv.CapturedDecodeStep(devc, qs, ks, vs, outs, max_replays=steps, peers=peers)
+    assert [c.kv_seq_len for c in devc] == [L0 + 1] * layers          # capturing moved nothing
+    worst = 0.0
+    for i in range(steps):
+        t = L0 + 1 + i
+        want = []
+        for l in range(layers):
+            q = _t(make_q(2000 + 7 * i + l, B, nh), cuda)
+            qs[l].copy_(q); ks[l].copy_(kt[:, :, t:t + 1]); vs[l].copy_(vt[:, :, t:t + 1])
+            want.append(host[l].decode_step(q, kt[:, :, t:t + 1], vt[:, :, t:t + 1]))
+        step.replay()
+        torch.cuda.synchronize()
+        for l in range(layers):
+            worst = max(worst, float(row_rel(outs[l].cpu().numpy(), want[l].cpu().numpy()).max()))
+            if peers is not None and l >= layers - peers.depth:  # the round-robin gather buffers still hold the last layers
+                assert torch.equal(step.gathered[l], outs[l])
+    assert worst <= 1e-3, worst
+    if peers is not None:
+        peers.check()
+    for h, d in zip(host, devc):
+        assert (h.kv_seq_len, h.tkq, h.tvq, h.k_start, h.v_start) == (d.kv_seq_len, d.tkq, d.tvq, d.k_start, d.v_start)
+        assert d.state.tolist()[:5] == [h.kv_seq_len, h.tkq, h.tvq, h.k_start, h.v_start]
+        for x, y in zip(d.as_tuple()[:8], h.as_tuple()[:8]):
+            assert torch.equal(x, y)
+    with pytest.raises(RuntimeError, match="beyond the context"):
+        step.replay()

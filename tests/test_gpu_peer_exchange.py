@@ -62,3 +62,24 @@ def test_wait_gives_up_and_reports(cuda):
     assert status.tolist() == [0, 0]                             # already there: no report, and the context still works
     assert L.kvq_peer_wait(None, 5, 2000, C.c_void_p(status.data_ptr()), stream) == -10
     assert L.kvq_peer_wait(C.c_void_p(cnt.data_ptr()), 5, 0, C.c_void_p(status.data_ptr()), stream) == -7
+
+
+def test_generation_wait(cuda):
+    """kvq_peer_wait_next keeps the target on the device: use g of a counter waits for g * per_use arrivals."""
+    from kvmix_b200 import _lib
+    L = _lib.lib()
+    cnt = torch.zeros(1, dtype=torch.int32, device=cuda)
+    gen = torch.zeros(1, dtype=torch.int32, device=cuda)
+    status = torch.zeros(2, dtype=torch.int32, device=cuda)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    cnt.fill_(8)                                                 # two uses' worth of arrivals are already there
+    for use in (1, 2):
+        assert L.kvq_peer_wait_next(p(cnt), 4, p(gen), 2000, p(status), stream) == 0
+        torch.cuda.synchronize()
+        assert gen.item() == use and status.tolist() == [0, 0]
+    assert L.kvq_peer_wait_next(p(cnt), 4, p(gen), 2000, p(status), stream) == 0      # the third use never arrives
+    torch.cuda.synchronize()
+    assert gen.item() == 3 and status.tolist() == [1, 8]
+    assert L.kvq_peer_wait_next(None, 4, p(gen), 2000, p(status), stream) == -10
+    assert L.kvq_peer_wait_next(p(cnt), 0, p(gen), 2000, p(status), stream) == -7
