@@ -533,7 +533,8 @@ def main():
     eager_events, attn_events = attn_events, []
     captured = None
     if args.graph != "off":
-        ok = all(c._fused is True and c.steady() for c in caches)
+        # (the NCCL exchange is launched by torch between the layers; it stays a host-driven step)
+        ok = all(c._fused is True and c.steady() for c in caches) and (not head_sharded or peer is not None)
         if world > 1:
             flag = torch.tensor([int(ok)], device=dev)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
