@@ -530,6 +530,8 @@ def main():
         step_device(False)
     step_device(True)                      # the last warm-up step, launch by launch with CUDA events around each layer
     torch.cuda.synchronize()
+    if peer is not None:
+        peer.check()                       # an exchange that does not arrive stops the run here, not after K slow steps
     eager_events, attn_events = attn_events, []
     captured = None
     if args.graph != "off":
