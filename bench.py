@@ -34,6 +34,7 @@ DTYPE = "f16 data, f32 accumulate, u32 packed codes"
 
 # dram__bytes_read + dram__bytes_write over algorithmic bytes of one fused-attention launch, from the ncu captures
 # summarised in profiles/decode_attn_mma_kernel_B32_ctx4096.md (one CTA per head there, so the ratio carries over).
+EAGER_SAMPLE_STEPS = 8
 NCU_TRAFFIC_RATIO = {(4, 4): 1.056, (3, 2): 1.049, (2, 2): 1.051}
 
 
@@ -424,7 +425,7 @@ def main():
         b_lo, b_hi = sharding.shard_batch(cfg.batch, world, rank)
         B, nh, hkv = b_hi - b_lo, cfg.n_heads, cfg.n_kv_heads
 
-    caches = configs.build_layer_caches(cfg, B, dev, extra_tokens=3 * (W + K) + 24, kv_heads=hkv, seed=rank,
+    caches = configs.build_layer_caches(cfg, B, dev, extra_tokens=3 * (W + K) + 24 + EAGER_SAMPLE_STEPS, kv_heads=hkv, seed=rank,
                                         device_state=args.graph != "off")
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     mk = lambda h: torch.randn((B, h, 1, D), generator=g, device=dev, dtype=torch.float16)
@@ -526,9 +527,10 @@ def main():
         return float(ms.item())
 
     # device-resident run -------------------------------------------------------------------------
-    for _ in range(W - 1):
+    for _ in range(W):
         step_device(False)
-    step_device(True)                      # the last warm-up step, launch by launch with CUDA events around each layer
+    for _ in range(EAGER_SAMPLE_STEPS):    # launch by launch with CUDA events around each layer: the per-bit-setting figures
+        step_device(True)                  # of a run whose timed region is a graph replay (no events inside a graph)
     torch.cuda.synchronize()
     if peer is not None:
         peer.check()                       # an exchange that does not arrive stops the run here, not after K slow steps
@@ -637,7 +639,7 @@ def main():
                          "timed_launch_is": "one decode step of one layer: ring append + (when due) group quantization + attention",
                          "launch_timing": ("CUDA events around the K replays of the step graph, divided by its attention launches "
                                            "(no events inside a graph: gaps and exchange waits are included); per_bit_setting "
-                                           "comes from the last warm-up step, launched layer by layer with events"
+                                           f"comes from {EAGER_SAMPLE_STEPS} untimed steps before it, launched layer by layer with events"
                                            if captured is not None else "CUDA events around every launch of the timed region"),
                          "per_bit_setting": {f"K{kb}V{vb}": {"us": t[0] * 1e3 / t[2], "GBs": t[1] / (t[0] * 1e-3) / 1e9}
                                              for (kb, vb), t in sorted(per_kind.items())},
