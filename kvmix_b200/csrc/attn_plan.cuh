@@ -27,6 +27,11 @@ struct AttnPlan {
 };
 
 constexpr int kSmCount = 148;
+// One partial result of a cut head: 128 accumulators, the segment's maximum and sum, padded so that rows stay 16-byte
+// aligned (the merge reads them with 128-bit loads).
+constexpr int kPartStride = 128 + 4;
+// What merging one more segment costs the CTA that finishes last, in tokens' worth of time.
+constexpr int kMergeTokensPerSegment = 8;
 // A CTA costs about this many tokens' worth of time besides the tokens it scores (launch, ring fill of two phases,
 // softmax barriers, warps that get one key tile fewer than their neighbours, merge).  Measured on B200 with 2-bit
 // keys and values at 4096 tokens: 256 heads take 54 us whole, 60 .. 66 us cut in 2 .. 4 (more CTAs than resident
@@ -37,7 +42,9 @@ constexpr int kMaxCtaRounds = 8;       // cut heads are never spread over more C
 
 // heads: number of heads (or head groups); max_chunk: most tokens a segment may hold (score buffer); slots: resident
 // CTAs on the whole GPU.
-inline AttnPlan make_attn_plan(int T, int unit, int max_chunk, long long heads, int slots) {
+// units_per_pass: units the warps of a CTA work side by side (4 when a unit is one warp's key tile, 1 when a unit is
+// already a tile per warp): a segment takes as long as its units rounded up to that.
+inline AttnPlan make_attn_plan(int T, int unit, int max_chunk, long long heads, int slots, int units_per_pass = 1) {
     AttnPlan p;
     p.unit = unit;
     p.uph = (T + unit - 1) / unit;
@@ -56,8 +63,10 @@ inline AttnPlan make_attn_plan(int T, int unit, int max_chunk, long long heads, 
             const long long ctas = (long long)p.n_cut * k;
             if (ctas > (long long)kMaxCtaRounds * slots && best >= 0) break;
             const long long rounds = (ctas + slots - 1) / slots;
-            const long long tokens = (long long)su * unit < T ? (long long)su * unit : T;
-            const long long cost = rounds * (tokens + kCtaOverheadTokens) + (k > 1 ? kCtaOverheadTokens / 4 : 0);
+            const long long su_eff = (long long)(su + units_per_pass - 1) / units_per_pass * units_per_pass;
+            const long long tokens = k > 1 ? su_eff * unit : ((long long)su * unit < T ? (long long)su * unit : T);
+            const long long cost = rounds * (tokens + kCtaOverheadTokens) +
+                                   (k > 1 ? kCtaOverheadTokens / 4 + (long long)k * kMergeTokensPerSegment : 0);
             if (best < 0 || cost < best) {
                 best = cost;
                 p.k = k;

@@ -19,7 +19,6 @@ namespace kvq {
 
 constexpr int kAttnThreads = 256;
 constexpr int kMaxChunk = 4224;  // tokens per split held in shared memory (multiple of 128 and of 352)
-constexpr int kPartStride = kHeadDim + 2;
 
 struct SplitPlan {
     int chunk, n_splits;

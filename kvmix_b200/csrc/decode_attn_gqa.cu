@@ -674,7 +674,7 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, const kvq_at
     __syncthreads();
 
     // ---- 4. finish / merge: thread tid owns channel tid of every head ----------------------------------
-    constexpr int kPart = kHeadDim + 2;
+    constexpr int kPart = kPartStride;
     float o[kQH];
 #pragma unroll
     for (int hs = 0; hs < kQH; ++hs) {
@@ -716,74 +716,41 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, const kvq_at
     }
     __syncthreads();
     if (sm.misc[8] == 0.f) return;
-    // The last CTA merges the cnt segments of its head group.  A long context over few heads means hundreds of segments,
-    // so the merge keeps many loads in flight instead of walking the segments one dependent round trip at a time:
-    // the maxima first (thread t looks at segments t, t + 128, ...), then warp w sums segments w, w + 4, ... with lane
-    // l owning channels 2l, 2l + 1, 64 + 2l, 65 + 2l of every head; the four warps' sums meet in shared memory in warp
-    // order.  The mapping is fixed, so results are run-to-run identical.
-    const float *base = parts + (int64_t)(s - n_whole) * cnt * qhv * kPart;
-    const int stride = qhv * kPart;
-    float M[kQH];
-#pragma unroll
-    for (int hs = 0; hs < kQH; ++hs) M[hs] = kMaskFloor;
-    for (int i = tid; i < cnt; i += kMmaThreads) {
-#pragma unroll
-        for (int hs = 0; hs < kQH; ++hs)
-            if (hs < qhv) M[hs] = fmaxf(M[hs], __ldcg(base + (int64_t)i * stride + hs * kPart + kHeadDim));
-    }
-#pragma unroll
-    for (int hs = 0; hs < kQH; ++hs) {
-        M[hs] = warp_max(M[hs]);
-        if (lane == 0) sm.misc[16 + warp * kQH + hs] = M[hs];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int hs = 0; hs < kQH; ++hs) {
-        M[hs] = sm.misc[16 + hs];
-#pragma unroll
-        for (int w = 1; w < kMmaWarps; ++w) M[hs] = fmaxf(M[hs], sm.misc[16 + w * kQH + hs]);
-    }
-    float2 acc0[kQH], acc1[kQH];
-    float Ls[kQH];
-#pragma unroll
-    for (int hs = 0; hs < kQH; ++hs) { acc0[hs] = make_float2(0.f, 0.f); acc1[hs] = make_float2(0.f, 0.f); Ls[hs] = 0.f; }
-#pragma unroll 2
-    for (int i = warp; i < cnt; i += kMmaWarps) {
-        const float *pi = base + (int64_t)i * stride;
-#pragma unroll
-        for (int hs = 0; hs < kQH; ++hs) {
-            if (hs < qhv) {
-                const float w = __expf(__ldcg(pi + hs * kPart + kHeadDim) - M[hs]);
-                Ls[hs] = fmaf(__ldcg(pi + hs * kPart + kHeadDim + 1), w, Ls[hs]);
-                const float2 p0 = __ldcg(reinterpret_cast<const float2 *>(pi + hs * kPart) + lane);
-                const float2 p1 = __ldcg(reinterpret_cast<const float2 *>(pi + hs * kPart + 64) + lane);
-                acc0[hs].x = fmaf(p0.x, w, acc0[hs].x); acc0[hs].y = fmaf(p0.y, w, acc0[hs].y);
-                acc1[hs].x = fmaf(p1.x, w, acc1[hs].x); acc1[hs].y = fmaf(p1.y, w, acc1[hs].y);
-            }
+    // The last CTA merges the cnt segments of its head group.  A long context over few heads means a hundred or more
+    // segments, and a merge that walks them one dependent round trip at a time becomes the kernel, so many 128-bit loads
+    // are kept in flight: warp w merges head slot w, lane l owning channels 4l .. 4l + 3; the maximum over the segments
+    // first (lanes over segments), then the weighted sums, eight segments' loads issued before the first is used.  The
+    // order is fixed, so results are run-to-run identical.
+    __half *stage = reinterpret_cast<__half *>(after_scores);             // [kQH][128] results, regions are idle by now
+    if (warp < qhv) {
+        const float *bh = parts + (int64_t)(s - n_whole) * cnt * qhv * kPart + warp * kPart;
+        const int stride = qhv * kPart;
+        float M = kMaskFloor;
+        for (int i = lane; i < cnt; i += 32) M = fmaxf(M, __ldcg(bh + (int64_t)i * stride + kHeadDim));
+        M = warp_max(M);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < cnt; ++i) {
+            const float *pi = bh + (int64_t)i * stride;
+            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(pi + kHeadDim));
+            const float4 p = __ldcg(reinterpret_cast<const float4 *>(pi) + lane);
+            const float w = __expf(ml.x - M);
+            L = fmaf(ml.y, w, L);
+            acc.x = fmaf(p.x, w, acc.x); acc.y = fmaf(p.y, w, acc.y);
+            acc.z = fmaf(p.z, w, acc.z); acc.w = fmaf(p.w, w, acc.w);
         }
-    }
-    {   // this warp's sums into its own (now idle) region: [kQH][128] floats, then kQH sums
-        float *mine = reinterpret_cast<float *>(sm.ring);
-#pragma unroll
-        for (int hs = 0; hs < kQH; ++hs) {
-            reinterpret_cast<float2 *>(mine + hs * kHeadDim)[lane] = acc0[hs];
-            reinterpret_cast<float2 *>(mine + hs * kHeadDim + 64)[lane] = acc1[hs];
-            if (lane == 0) mine[kQH * kHeadDim + hs] = Ls[hs];
-        }
+        const float inv = 1.f / L;
+        __half2 *dst = reinterpret_cast<__half2 *>(stage + warp * kHeadDim + 4 * lane);
+        dst[0] = __floats2half2_rn(acc.x * inv, acc.y * inv);
+        dst[1] = __floats2half2_rn(acc.z * inv, acc.w * inv);
     }
     __syncthreads();
 #pragma unroll
     for (int hs = 0; hs < kQH; ++hs) {
         if (hs < qhv) {
-            float acc = 0.f, L = 0.f;
-#pragma unroll
-            for (int w = 0; w < kMmaWarps; ++w) {
-                const float *reg = reinterpret_cast<const float *>(after_scores + w * kRegion);
-                acc += reg[hs * kHeadDim + tid];
-                L += reg[kQH * kHeadDim + hs];
-            }
             __half *out = static_cast<__half *>(a.out) + (int64_t)b * a.o_sB + (int64_t)(h_first + hs) * a.o_sH;
-            res[hs] = __float2half_rn(acc / L);
+            res[hs] = stage[hs * kHeadDim + tid];
             out[tid] = res[hs];
         }
     }
@@ -828,7 +795,7 @@ int gqa_heads_per_cta(const kvq_attn_args &a) {
 AttnPlan plan_attn_gqa(int T, int k_bits, long long head_groups) {
     const int unit = (k_bits == 3) ? 352 : 256;
     const int max_chunk = (k_bits == 3) ? 2816 : kGqaMaxChunk;     // whole units of 352 / 256 tokens
-    return make_attn_plan(T, unit, max_chunk, head_groups, kSmCount * 2);
+    return make_attn_plan(T, unit, max_chunk, head_groups, kSmCount * 2, k_bits == 3 ? 1 : kMmaWarps);
 }
 
 template <int KB, int VB>

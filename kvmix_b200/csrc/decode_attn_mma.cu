@@ -754,7 +754,7 @@ __device__ __forceinline__ void attn_segment(const kvq_attn_args &a, const kvq_a
         peer_publish(ac, b, h, 1, r, tid);
         return;
     }
-    constexpr int kPart = kHeadDim + 2;
+    constexpr int kPart = kPartStride;
     float *part = parts + ((int64_t)(s - n_whole) * cnt + seg) * kPart;          // partials of the cut heads only
     part[tid] = o;
     if (tid == 0) { part[kHeadDim] = m; part[kHeadDim + 1] = l; }
@@ -871,7 +871,7 @@ int launch_decode_attn_mma(const kvq_attn_args &a, const AttnPlan &plan, float *
 AttnPlan plan_attn_mma(int T, int k_bits, long long heads) {
     const int unit = (k_bits == 3) ? 352 : 256;              // one key tile per warp
     const int max_chunk = (k_bits == 3) ? 8096 : 8192;       // scores held in shared memory
-    return make_attn_plan(T, unit, max_chunk, heads, kSmCount * 3);
+    return make_attn_plan(T, unit, max_chunk, heads, kSmCount * 3, k_bits == 3 ? 1 : kMmaWarps);
 }
 
 }  // namespace kvq
