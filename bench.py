@@ -365,6 +365,10 @@ def main():
     ap.add_argument("--context", type=int, default=None, help="override the context length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-upstream-gpu", action="store_true")
+    ap.add_argument("--one-shard-of", type=int, default=1, metavar="N",
+                    help="run ONE rank's share of an N-GPU run on this GPU, without the exchange (a kernel-side view of the "
+                         "sharded shapes: 1/N of the kv heads of a head-sharded configuration, 1/N of the batch otherwise); the "
+                         "line's value is that one shard's tokens/s")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="device-resident leg: replay the whole decode step (every layer's fused launch, and the exchange waits "
                          "of a head-sharded run) from one CUDA graph with the cache lengths held on the device; auto = when "
@@ -398,6 +402,12 @@ def main():
         cfg.batch = args.batch
     if args.context:
         cfg.context = args.context
+    if args.one_shard_of > 1:
+        if cfg.shard == "kv_head":
+            cfg.n_heads, cfg.n_kv_heads = cfg.n_heads // args.one_shard_of, cfg.n_kv_heads // args.one_shard_of
+        else:
+            cfg.batch = cfg.batch // args.one_shard_of
+        cfg.name += f"-one-shard-of-{args.one_shard_of}"
     if args.impl == "reference":
         return run_reference(args, cfg)
 

@@ -31,7 +31,7 @@ constexpr int kSmCount = 148;
 // aligned (the merge reads them with 128-bit loads).
 constexpr int kPartStride = 128 + 4;
 // What merging one more segment costs the CTA that finishes last, in tokens' worth of time.
-constexpr int kMergeTokensPerSegment = 8;
+constexpr int kMergeTokensPerSegment = 4;
 // A CTA costs about this many tokens' worth of time besides the tokens it scores (launch, ring fill of two phases,
 // softmax barriers, warps that get one key tile fewer than their neighbours, merge).  Measured on B200 with 2-bit
 // keys and values at 4096 tokens: 256 heads take 54 us whole, 60 .. 66 us cut in 2 .. 4 (more CTAs than resident

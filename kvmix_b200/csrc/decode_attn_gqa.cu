@@ -719,7 +719,7 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, const kvq_at
     // The last CTA merges the cnt segments of its head group.  A long context over few heads means a hundred or more
     // segments, and a merge that walks them one dependent round trip at a time becomes the kernel, so many 128-bit loads
     // are kept in flight: warp w merges head slot w, lane l owning channels 4l .. 4l + 3; the maximum over the segments
-    // first (lanes over segments), then the weighted sums, eight segments' loads issued before the first is used.  The
+    // first (lanes over segments), then the weighted sums, sixteen segments' loads issued before the first is used.  The
     // order is fixed, so results are run-to-run identical.
     __half *stage = reinterpret_cast<__half *>(after_scores);             // [kQH][128] results, regions are idle by now
     if (warp < qhv) {
@@ -730,7 +730,7 @@ __device__ __forceinline__ void gqa_segment(const kvq_attn_args &a, const kvq_at
         M = warp_max(M);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         float L = 0.f;
-#pragma unroll 8
+#pragma unroll 16
         for (int i = 0; i < cnt; ++i) {
             const float *pi = bh + (int64_t)i * stride;
             const float2 ml = __ldcg(reinterpret_cast<const float2 *>(pi + kHeadDim));
