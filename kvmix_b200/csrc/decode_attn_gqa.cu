@@ -10,7 +10,9 @@
 //           per-lane byte permute and mask.  The zero term sum_d q_h[d] * zero[d, group] comes from MMAs whose A operand
 //           has ones in a single row (row = group), so all groups of a tile share one accumulator.
 //   values  column 2h / 2h+1 = p_h[t] * scale[t, group] / p_h[t] * midpoint[t, group]; an MMA's 16 channel rows lie
-//           in one channel group (a 16-byte block of a token row = 128 / 64 / 32 channels; needs v_group >= that).
+//           in one channel group (a 16-byte block of a token row = 128 / 64 / 32 channels; needs v_group >= that --
+//           except 1-bit values at group 64, where a block spans two groups and every code tile is multiplied by both
+//           groups' operands, each lane keeping the product of the group its rows belong to).
 // Scores of the four heads sit side by side in shared memory ([4][n]); warp w runs the softmax of head w.
 #include "attn_mma_common.cuh"
 #include "attn_plan.cuh"
@@ -409,6 +411,13 @@ __device__ __forceinline__ void gqa_pv_packed(const kvq_attn_args &a, const int3
     float acc[8][4], accz[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};    // ones-MMAs alternate between two accumulators
 #pragma unroll
     for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+    // 1-bit values in groups of 64 channels: a 16-byte block (128 channels) then spans two groups, and the rows of an
+    // MMA (lane octet g = channels 16 g .. 16 g + 15) lie in group g / 4.  Every code tile is multiplied twice, by the
+    // operands of group 0 and of group 1, and a lane keeps the product of its own group.
+    const bool split = VB == 1 && Gv == 64;
+    float acc2[VB == 1 ? 8 : 1][4];
+#pragma unroll
+    for (int m = 0; m < (VB == 1 ? 8 : 1); ++m) acc2[m][0] = acc2[m][1] = acc2[m][2] = acc2[m][3] = 0.f;
     const uint32_t ones = 0x3c003c00u;
     constexpr int kFlush = 16;                                 // short accumulation chains (see the single-head kernel)
     float sum[8][2], sumz[2] = {0.f, 0.f};
@@ -417,8 +426,15 @@ __device__ __forceinline__ void gqa_pv_packed(const kvq_attn_args &a, const int3
     auto flush = [&]() {
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
-            sum[m][0] += acc[m][0];
-            sum[m][1] += acc[m][2];
+            if constexpr (VB == 1) {
+                const bool second = split && g >= 4;
+                sum[m][0] += second ? acc2[m][0] : acc[m][0];
+                sum[m][1] += second ? acc2[m][2] : acc[m][2];
+                acc2[m][0] = acc2[m][1] = acc2[m][2] = acc2[m][3] = 0.f;
+            } else {
+                sum[m][0] += acc[m][0];
+                sum[m][1] += acc[m][2];
+            }
             acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
         }
         sumz[0] += accz[0][0] + accz[1][0];
@@ -501,6 +517,13 @@ __device__ __forceinline__ void gqa_pv_packed(const kvq_attn_args &a, const int3
 #pragma unroll
                 for (int i = 0; i < F::N; i += 2)
                     mma16816(acc[bb * MPB + i / 2], rlo[i], rlo[i + 1], rhi[i], rhi[i + 1], bx, by);
+                if constexpr (VB == 1) {
+                    if (split) {
+#pragma unroll
+                        for (int i = 0; i < F::N; i += 2)
+                            mma16816(acc2[i / 2], rlo[i], rlo[i + 1], rhi[i], rhi[i + 1], b[1][0], b[1][1]);
+                    }
+                }
             }
         }
         __syncwarp();
@@ -522,7 +545,8 @@ __device__ __forceinline__ void gqa_pv_packed(const kvq_attn_args &a, const int3
 #pragma unroll
     for (int bb = 0; bb < NB; ++bb) {
         const int c0 = bb * CPB + g * F::N;
-        const float corr = Gv == 32 ? cj[(bb * CPB) / 32 < 4 ? (bb * CPB) / 32 : 3] : Gv == 64 ? cj[(bb * CPB) / 64] : cj[0];
+        const float corr = Gv == 32 ? cj[(bb * CPB) / 32 < 4 ? (bb * CPB) / 32 : 3]
+                         : Gv == 64 ? (VB == 1 ? (g >= 4 ? cj[1] : cj[0]) : cj[(bb * CPB) / 64]) : cj[0];
 #pragma unroll
         for (int ip = 0; ip < MPB; ++ip) {
             my_red[tig * kHeadDim + c0 + 2 * ip] = fmaf(sum[bb * MPB + ip][0], (float)(1 << (16 - F::pos(2 * ip))), corr);
@@ -786,7 +810,7 @@ int gqa_heads_per_cta(const kvq_attn_args &a) {
     const int n_rep = a.nh / a.nh_kv;
     if (n_rep != 2 && n_rep % 4 != 0) return 0;
     const int kmin = a.k_bits == 1 ? 128 : a.k_bits == 2 ? 64 : a.k_bits == 4 ? 64 : 11;
-    const int vmin = a.v_bits == 1 ? 128 : a.v_bits == 2 ? 64 : 32;
+    const int vmin = a.v_bits == 1 ? 64 : a.v_bits == 2 ? 64 : 32;     // 1-bit values at group 64: two MMAs per code tile
     if (a.k_bits != 3 && a.k_group < kmin) return 0;
     if (a.v_group < vmin) return 0;
     return n_rep == 2 ? 2 : 4;

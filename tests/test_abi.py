@@ -122,7 +122,7 @@ def test_split_plan_invariants_and_workspace_bound():
                     assert g.kernel == 0 and g.unit > 0 and g.segments >= 1
                     assert (g.segments - 1) * g.unit < T <= g.segments * g.unit <= g.segments * 4224
                     assert g.unit % (352 if kb == 3 else 128) == 0 and g.n_ctas == heads * g.segments
-                    need = 0 if g.segments == 1 else ((heads * 4 + 255) // 256) * 256 + heads * g.segments * 130 * 4
+                    need = 0 if g.segments == 1 else ((heads * 4 + 255) // 256) * 256 + heads * g.segments * 132 * 4
                     assert need <= ws
                     p = _plan(B, nh, T, kb, 1, nh_kv, 128)
                     grouped = nh // nh_kv in (2, 4, 8)
@@ -143,7 +143,7 @@ def test_split_plan_invariants_and_workspace_bound():
                         for segs in seen.values():
                             assert segs[0][0] == 0 and segs[-1][1] == T and len(segs) == segs[0][2]
                     partials = 0 if p.segments == 1 else p.n_cut * p.segments * p.heads_per_cta
-                    need = 0 if partials == 0 else ((heads * 4 + 255) // 256) * 256 + partials * 130 * 4
+                    need = 0 if partials == 0 else ((heads * 4 + 255) // 256) * 256 + partials * 132 * 4
                     assert need <= ws, (B, nh, nh_kv, Tmax, T, kb, p.kernel, p.segments)
 
 
@@ -158,5 +158,8 @@ def test_split_plan_prefers_one_split_for_full_grids():
     p = _plan(8, 32, 32768, 2, 1, nh_kv=8, G=64)             # grouped queries: 64 head groups of 4 query heads
     assert (p.kernel, p.heads_per_cta, p.n_whole + p.n_cut) == (2, 4, 64) and p.max_segment_tokens <= 2048
     assert _plan(8, 32, 32768, 2, 1, nh_kv=8, G=32).kernel == 1      # 2-bit keys in groups of 32: one head per CTA
+    assert _plan(8, 32, 32768, 2, 1, nh_kv=8, G=64, vb=1).kernel == 2     # 1-bit values at group 64: two groups per block
+    assert _plan(8, 32, 32768, 4, 1, nh_kv=8, G=64, vb=2).kernel == 2
+    assert _plan(8, 32, 32768, 4, 1, nh_kv=8, G=32, vb=2).kernel == 1     # 2-bit values at group 32: one head per CTA
     with pytest.raises(Exception):
         _lib.check(_lib.lib().kvq_decode_attn_plan(None, 1, None))
