@@ -35,7 +35,7 @@ DTYPE = "f16 data, f32 accumulate, u32 packed codes"
 # dram__bytes_read + dram__bytes_write over algorithmic bytes of one fused-attention launch, from the ncu captures
 # summarised in profiles/decode_attn_mma_kernel_B32_ctx4096.md (one CTA per head there, so the ratio carries over).
 EAGER_SAMPLE_STEPS = 8
-NCU_TRAFFIC_RATIO = {(4, 4): 1.056, (3, 2): 1.049, (2, 2): 1.051}
+NCU_TRAFFIC_RATIO = {(4, 4): 1.042, (3, 2): 1.082, (2, 2): 1.058}    # fused decode step, device-driven (the bench's launches)
 
 
 def measured_peak_gbs():
@@ -643,7 +643,7 @@ def main():
                          "unit": "GB/s", "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "peak_source": peak_src, "traffic": traffic,
                          "traffic_note": "bytes per launch (layer average): algorithmic bytes of this run x the ncu dram "
-                                         "read+write / algorithmic ratio of profiles/decode_attn_mma_kernel_B32_ctx4096.md",
+                                         "read+write / algorithmic ratio of profiles/decode_attn_mma_kernel_B32_ctx4096.md (the fused decode step there)",
                          "bytes_per_launch": attn_bytes_all / max(1, n_attn),
                          "us_per_launch": attn_ms_all * 1e3 / max(1, n_attn), "launches_timed": n_attn,
                          "timed_launch_is": "one decode step of one layer: ring append + (when due) group quantization + attention",

@@ -2,6 +2,8 @@
 under profiles/ run.
 
     python -m kvmix_b200.microbench attn  KB VB G [B] [T] [reps] [heads] [kv_heads] [window]   one layer of fused decode attention
+    python -m kvmix_b200.microbench step  KB VB G [B] [T] [reps] [heads] [kv_heads] [window]   one layer's fused decode step:
+                                                                        append + quantize when due + attention, device-driven
     python -m kvmix_b200.microbench quant BITS G STYLE [B] [T] [reps]   STYLE k: [B,32,T,128] keys, groups over tokens
                                                                         STYLE v: values, groups over channels
     python -m kvmix_b200.microbench gemv  BITS G [B] [T] [reps]         the stand-alone quantized_gemm (q.K^T form)
@@ -42,6 +44,27 @@ def attn(kb, vb, G, B=16, T=4096, reps=3, heads=32, kv_heads=None, window=128):
     ms = _time(lambda: c.attend(q, out=out), reps)
     by = c.packed_bytes() + 2 * B * heads * 128 * 2
     print(f"attn K{kb}V{vb} G{G} B{B} H{heads}/{kv_heads} T{T}: {ms * 1e3:.1f} us/launch, {by / 1e6:.1f} MB, "
+          f"{by / ms / 1e6:.0f} GB/s")
+    return by / ms / 1e6
+
+
+def step(kb, vb, G, B=16, T=4096, reps=3, heads=32, kv_heads=None, window=128):
+    """The product's per-layer launch: one fused decode step with the cache lengths read from device memory."""
+    dev = torch.device("cuda:0")
+    kv_heads = kv_heads or heads
+    c = KVmixLayerCache(B, kv_heads, 128, T + 2 * reps + 64, kb, vb, G, residual_length=window, device=dev, device_state=True)
+    k, v = configs.synth_kv(B, kv_heads, T, 128, dev, 0)
+    c.prefill(k, v)
+    del k, v
+    q = torch.randn((B, heads, 1, 128), device=dev, dtype=torch.float16)
+    kn = torch.randn((B, kv_heads, 1, 128), device=dev, dtype=torch.float16)
+    vn = torch.randn((B, kv_heads, 1, 128), device=dev, dtype=torch.float16)
+    out = torch.empty_like(q)
+    ms = _time(lambda: c.decode_step(q, kn, vn, out=out), reps)
+    if c._fused is not True:
+        raise SystemExit("this geometry is not served by the fused decode step")
+    by = c.packed_bytes() + 2 * B * heads * 128 * 2
+    print(f"step K{kb}V{vb} G{G} B{B} H{heads}/{kv_heads} T{T}: {ms * 1e3:.1f} us/launch, {by / 1e6:.1f} MB, "
           f"{by / ms / 1e6:.0f} GB/s")
     return by / ms / 1e6
 
@@ -97,6 +120,8 @@ if __name__ == "__main__":
         raise SystemExit(__doc__)
     if a[0] == "attn":
         attn(*[int(x) for x in a[1:]])
+    elif a[0] == "step":
+        step(*[int(x) for x in a[1:]])
     elif a[0] == "quant":
         quant(int(a[1]), int(a[2]), a[3], *[int(x) for x in a[4:]])
     elif a[0] == "gemv":
