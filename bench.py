@@ -32,9 +32,10 @@ SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.acti
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 DTYPE = "f16 data, f32 accumulate, u32 packed codes"
 
+# untimed steps launched layer by layer with events before a graph-replayed timed region (per-bit-setting figures)
+EAGER_SAMPLE_STEPS = 8
 # dram__bytes_read + dram__bytes_write over algorithmic bytes of one fused-attention launch, from the ncu captures
 # summarised in profiles/decode_attn_mma_kernel_B32_ctx4096.md (one CTA per head there, so the ratio carries over).
-EAGER_SAMPLE_STEPS = 8
 NCU_TRAFFIC_RATIO = {(4, 4): 1.042, (3, 2): 1.082, (2, 2): 1.058}    # fused decode step, device-driven (the bench's launches)
 
 
