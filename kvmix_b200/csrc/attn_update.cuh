@@ -122,7 +122,7 @@ __device__ __forceinline__ const __half *v_tail_row(const kvq_attn_args &a, cons
 // Device-resident cache state (kvq_attn_args.state): five ints {T, Tkq, Tvq, kf_start, vf_start} describing the cache
 // BEFORE this step, a completion counter at [5].  The kernel applies upstream's window policy itself -- keep
 // `window` tokens in fp16, or int(ratio * current_fp16_len) (models/modeling_llama_KVmix.py:118-126) -- to derive
-// what this step does, and the CTA that finishes last writes the state after the step back, so the launch arguments
+// what this step does, and the last CTA to have read the state writes the state after the step back, so the launch arguments
 // of a decode loop never change and a whole step can be replayed from a CUDA graph.  At most one group per step
 // becomes due in steady state; the host does not switch to this mode before that (upstream's ratio policy shrinks a
 // prompt's tail over several steps).
@@ -136,8 +136,20 @@ __device__ __forceinline__ int tokens_due(const kvq_attn_args &a, int cur, int g
 }
 
 __device__ __forceinline__ void dev_state_step(const kvq_attn_args &a, kvq_attn_args &b) {
-    const int *st = a.state;
-    const int T0 = st[0], Tkq0 = st[1], Tvq0 = st[2], ks0 = st[3], vs0 = st[4];
+    // One thread reads the state and counts the CTA in; the others take it from shared memory.  The state may be
+    // overwritten once every CTA of the grid has read it: the count is raised only after the reading thread holds the
+    // values (the branch on all five loaded values keeps it behind the loads), and the CTA that completes the count -- the last
+    // one to START, so nothing is left on the tail of the kernel -- publishes the state after the step (below).
+    __shared__ int s_state[5];
+    int *st = a.state;
+    bool publish = false;
+    if (threadIdx.x == 0) {
+        const int v0 = st[0], v1 = st[1], v2 = st[2], v3 = st[3], v4 = st[4];
+        s_state[0] = v0; s_state[1] = v1; s_state[2] = v2; s_state[3] = v3; s_state[4] = v4;
+        if ((v0 | v1 | v2 | v3 | v4) >= 0) publish = atomicAdd(reinterpret_cast<unsigned int *>(st + 5), 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    const int T0 = s_state[0], Tkq0 = s_state[1], Tvq0 = s_state[2], ks0 = s_state[3], vs0 = s_state[4];
     const int nk = tokens_due(a, T0 - Tkq0 + 1, a.k_group, a.k_ratio);
     const int nv = tokens_due(a, T0 - Tvq0 + 1, a.v_group, a.v_ratio);
     b.T = T0 + 1;
@@ -149,18 +161,9 @@ __device__ __forceinline__ void dev_state_step(const kvq_attn_args &a, kvq_attn_
     b.v_quant = nv;
     b.k_quant_slot = ks0;
     b.v_quant_slot = vs0;
-}
-
-// Every CTA calls this as its last action; the last one to arrive publishes the state after the step.
-__device__ __forceinline__ void dev_state_commit(const kvq_attn_args &b, int tid) {
-    __syncthreads();
-    if (tid == 0) {
-        int *st = b.state;
-        __threadfence();
-        if (atomicAdd(reinterpret_cast<unsigned int *>(st + 5), 1u) == gridDim.x - 1) {
-            st[0] = b.T; st[1] = b.Tkq; st[2] = b.Tvq; st[3] = b.kf_start; st[4] = b.vf_start;
-            st[5] = 0;
-        }
+    if (publish) {
+        st[0] = b.T; st[1] = b.Tkq; st[2] = b.Tvq; st[3] = b.kf_start; st[4] = b.vf_start;
+        st[5] = 0;
     }
 }
 

@@ -794,7 +794,6 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_attn_gqa_kernel(const _
         plan_cta(plan, b.T, blockIdx.x, group, t0, t1, seg, cnt);
         if (cnt > 1) cnt = min(cnt, (b.T + plan.seg_units * plan.unit - 1) / (plan.seg_units * plan.unit));
         if (t0 < b.T) gqa_segment<KB, VB>(b, a, plan.n_scores, qhv, group, t0, t1, seg, cnt, plan.n_whole, parts, counters);
-        dev_state_commit(b, threadIdx.x);
     } else {
         plan_cta(plan, a.T, blockIdx.x, group, t0, t1, seg, cnt);
         gqa_segment<KB, VB>(a, a, plan.n_scores, qhv, group, t0, t1, seg, cnt, plan.n_whole, parts, counters);

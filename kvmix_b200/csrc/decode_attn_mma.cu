@@ -798,7 +798,6 @@ __global__ void __launch_bounds__(kMmaThreads, 3) decode_attn_mma_kernel(const _
         plan_cta(plan, b.T, blockIdx.x, head, t0, t1, seg, cnt);
         if (cnt > 1) cnt = min(cnt, (b.T + plan.seg_units * plan.unit - 1) / (plan.seg_units * plan.unit));
         if (t0 < b.T) attn_segment<KB, VB>(b, a, plan.n_scores, head, t0, t1, seg, cnt, plan.n_whole, parts, counters);
-        dev_state_commit(b, threadIdx.x);
     } else {
         plan_cta(plan, a.T, blockIdx.x, head, t0, t1, seg, cnt);
         attn_segment<KB, VB>(a, a, plan.n_scores, head, t0, t1, seg, cnt, plan.n_whole, parts, counters);
