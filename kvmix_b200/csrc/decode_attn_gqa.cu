@@ -215,17 +215,26 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
 #pragma unroll
             for (int k = 0; k < G::KSPS; ++k) {
                 const int ksx = st * G::KSPS + k;
-                const __half2 q01 = as_h2(lds32(q_s + 32 * ksx)), q89 = as_h2(lds32(q_s + 32 * ksx + 16));
+                const uint32_t q01u = lds32(q_s + 32 * ksx), q89u = lds32(q_s + 32 * ksx + 16);
+                const __half2 q01 = as_h2(q01u), q89 = as_h2(q89u);
                 const uint32_t zrow = szrow_s + szbuf + 256 * ksx;   // scale rows 16 ksx + 2 tig (+1, +8, +9); zeros + ZOFF
                 if constexpr (KB == 3) {
-                    // every word is its own group: per word j one B operand, one code MMA (rows = its 11 tokens) and one
-                    // zero-term MMA (ones in row j); words are taken in pairs so that scales arrive as 32-bit loads
+                    // every word is its own group: per word j one B operand and one code MMA (rows = its 11 tokens); words
+                    // are taken in pairs so that scales arrive as 32-bit loads.  The zero terms sum_d q[d] * zero[d, j] of
+                    // all eight words come from ONE MMA per k-step: the zero tile ([channel][word], 16 bytes per channel)
+                    // read transposed is an A operand with row = word and k = channel, B = q in the even columns
+                    // (fp16 x fp16 products are exact in the tensor core, so no hi / lo split is needed here); a word
+                    // beyond the packed prefix only spoils its own row, which nothing reads
+                    {
+                        uint32_t za0, za2;
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
+                                     : "=r"(za0), "=r"(za2) : "r"(sz_s + szbuf + ZOFF + (16 * ksx + (lane & 15)) * 16));
+                        mma16816(accz[ksx & 3], za0, 0u, za2, 0u, q01u & ~neg_mask, q89u & ~neg_mask);
+                    }
 #pragma unroll
                     for (int jp = 0; jp < 4; ++jp) {
                         uint32_t sA = lds32(zrow + 4 * jp), sB = lds32(zrow + 16 + 4 * jp);
                         uint32_t sC = lds32(zrow + 128 + 4 * jp), sD = lds32(zrow + 144 + 4 * jp);
-                        uint32_t zA = lds32(zrow + ZOFF + 4 * jp), zB = lds32(zrow + ZOFF + 16 + 4 * jp);
-                        uint32_t zC = lds32(zrow + ZOFF + 128 + 4 * jp), zD = lds32(zrow + ZOFF + 144 + 4 * jp);
                         const uint32_t src = w3_s + stage_s + (k * 16) * G::RS + 8 * jp;
                         const uint2 wA = lds64(src), wB = lds64(src + G::RS), wC = lds64(src + 8 * G::RS), wD = lds64(src + 9 * G::RS);
 #pragma unroll
@@ -234,13 +243,10 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
                             if (jw >= nvg) continue;
                             const uint32_t psel = u ? 0x7632u : 0x5410u;
                             const __half2 s01 = as_h2(prmt(sA, sB, psel)), s89 = as_h2(prmt(sC, sD, psel));
-                            const __half2 z01 = as_h2(prmt(zA, zB, psel)), z89 = as_h2(prmt(zC, zD, psel));
                             const uint32_t a_lo = u ? wA.y : wA.x, b_lo = u ? wB.y : wB.x, a_hi = u ? wC.y : wC.x, b_hi = u ? wD.y : wD.x;
                             mma16816(acc[jw], prmt(a_lo, b_lo, sel0) & msk0, prmt(a_lo, b_lo, sel1) & msk1,
                                      prmt(a_hi, b_hi, sel0) & msk0, prmt(a_hi, b_hi, sel1) & msk1,
                                      hilo(q01, s01, neg_mask), hilo(q89, s89, neg_mask));
-                            const uint32_t row1 = (g == jw) ? ones : 0u;
-                            mma16816(accz[jw & 3], row1, 0u, row1, 0u, hilo(q01, z01, neg_mask), hilo(q89, z89, neg_mask));
                         }
                     }
                 } else {
