@@ -7,8 +7,9 @@
 //           rows therefore have to lie in ONE scale group: 1-, 2- and 4-bit keys are all fetched with transposing
 //           ldmatrix loads (a 16-byte block of a channel row = 128 / 64 / 32 tokens; needs k_group >= that), and
 //           3-bit keys (group 11 = one word) put the 11 tokens of a word in the rows of an MMA, extracting field g with a
-//           per-lane byte permute and mask.  The zero term sum_d q_h[d] * zero[d, group] comes from MMAs whose A operand
-//           has ones in a single row (row = group), so all groups of a tile share one accumulator.
+//           per-lane byte permute and mask.  The zero terms sum_d q_h[d] * zero[d, group] of all groups of a tile come
+//           from one MMA per 16 channels: the zero tile in shared memory ([channel][group]) read transposed is the A
+//           operand (row = group), q the B operand.
 //   values  column 2h / 2h+1 = p_h[t] * scale[t, group] / p_h[t] * midpoint[t, group]; an MMA's 16 channel rows lie
 //           in one channel group (a 16-byte block of a token row = 128 / 64 / 32 channels; needs v_group >= that --
 //           except 1-bit values at group 64, where a block spans two groups and every code tile is multiplied by both
@@ -181,7 +182,6 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
     __syncthreads();                                           // q is in shared memory (stored by the caller without a barrier)
     if (tail_lo < t1) gqa_qk_tail(a, kf, b, hk, sm, t0, tail_lo, t1);
 
-    const uint32_t ones = 0x3c003c00u;
     for (int j = 0; j < my_tiles; ++j) {
         const int tile0 = t0 + (j * kMmaWarps + warp) * G::WT;
         const bool have_next = j + 1 < my_tiles;
@@ -192,7 +192,7 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
         // groups of this tile that hold tokens below hi: operands of the others are never formed (their scale/zero
         // words lie beyond the packed prefix and may hold anything, and 0 * NaN would poison a shared accumulator)
         const int nvg = min(ngw, (hi - tile0 + Gk - 1) / Gk);
-        // the zero-term MMAs rotate over four accumulators so that consecutive ones do not wait for each other
+        // the zero-term MMAs (one per k-step) rotate over four accumulators so that consecutive ones do not wait for each other
         float acc[NACC][4], accz[4][4];
 #pragma unroll
         for (int m = 0; m < NACC; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
@@ -250,21 +250,27 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
                         }
                     }
                 } else {
-                    // B operands of the tile's groups (<= 4: k_group >= 64) and their zero terms
+                    // The zero terms sum_d q[d] * zero[d, j] of the tile's groups: one MMA per k-step whose A operand is the
+                    // scale/zero tile read transposed (a channel's 16-byte row holds 4 scales then 4 zeros, so rows 4..7
+                    // of the product are the zero terms of groups 0..3; rows 0..3 are not used) and whose B operand is
+                    // q in the even columns (fp16 x fp16 is exact in the tensor core).  A group beyond the packed prefix
+                    // only spoils its own row, which nothing reads.
+                    {
+                        uint32_t za0, za2;
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
+                                     : "=r"(za0), "=r"(za2) : "r"(sz_s + szbuf + (16 * ksx + (lane & 15)) * 16));
+                        mma16816(accz[ksx & 3], za0, 0u, za2, 0u, q01u & ~neg_mask, q89u & ~neg_mask);
+                    }
+                    // B operands of the tile's groups (<= 4: k_group >= 64)
                     const uint2 sA = lds64(zrow), sB = lds64(zrow + 16), sC = lds64(zrow + 128), sD = lds64(zrow + 144);
-                    const uint2 zA = lds64(zrow + ZOFF), zB = lds64(zrow + ZOFF + 16), zC = lds64(zrow + ZOFF + 128), zD = lds64(zrow + ZOFF + 144);
                     uint32_t b[4][2];
 #pragma unroll
                     for (int jk = 0; jk < 4; ++jk) {
                         if (jk < nvg) {
                             const uint32_t psel = (jk & 1) ? 0x7632u : 0x5410u;
                             const uint32_t a0 = (jk & 2) ? sA.y : sA.x, a1 = (jk & 2) ? sB.y : sB.x, a2 = (jk & 2) ? sC.y : sC.x, a3 = (jk & 2) ? sD.y : sD.x;
-                            const uint32_t c0 = (jk & 2) ? zA.y : zA.x, c1 = (jk & 2) ? zB.y : zB.x, c2 = (jk & 2) ? zC.y : zC.x, c3 = (jk & 2) ? zD.y : zD.x;
                             b[jk][0] = hilo(q01, as_h2(prmt(a0, a1, psel)), neg_mask);
                             b[jk][1] = hilo(q89, as_h2(prmt(a2, a3, psel)), neg_mask);
-                            const uint32_t row1 = (g == jk) ? ones : 0u;
-                            mma16816(accz[jk], row1, 0u, row1, 0u, hilo(q01, as_h2(prmt(c0, c1, psel)), neg_mask),
-                                     hilo(q89, as_h2(prmt(c2, c3, psel)), neg_mask));
                         } else {
                             b[jk][0] = b[jk][1] = 0u;
                         }
@@ -319,7 +325,7 @@ __device__ __forceinline__ void gqa_qk_packed(const kvq_attn_args &a, const int3
         } else {
             float zj[4];
 #pragma unroll
-            for (int jk = 0; jk < 4; ++jk) zj[jk] = __shfl_sync(0xffffffffu, zsum, 4 * jk + tig);
+            for (int jk = 0; jk < 4; ++jk) zj[jk] = __shfl_sync(0xffffffffu, zsum, 4 * (4 + jk) + tig);   // rows 4..7
 #pragma unroll
             for (int bb = 0; bb < NBK; ++bb) {
                 const float corr = wide ? zj[(bb * 8 * FH) / 128] : zj[(bb * 8 * FH) / 64];
