@@ -16,8 +16,9 @@
 //   A (16x16) = codes, rows = tokens, cols = 16 channels.  q[d]*scale[d,g] is carried as an exact fp16 pair hi + lo.
 //   A 256-token warp tile is worked as two halves whose MMA rows touch at most four groups, so B (16x8) holds
 //   {hi, lo} x 4 groups side by side and one MMA per code tile yields both parts.  3-bit keys (88-token tiles, every
-//   word its own group of 11) multiply each code tile by the hi and by the lo operand instead.  The zero term
-//   sum_d q[d]*zero[d,g] (hi and lo) is summed over channels by MMAs whose A operand is all ones.
+//   word its own group of 11) multiply each code tile by the hi and by the lo operand instead.  The zero terms
+//   sum_d q[d]*zero[d,g] of all groups of a tile come from one MMA per 16 channels whose A operand is the zero tile
+//   read transposed (row = group) and whose B operand is q.
 // Values (codes [T, D/fpi], one word = fpi channels of one token; scale/zero [T, D/G]):
 //   A (16x16) = codes, rows = channels, cols = 16 tokens;  B (16x8): column 2j = p[t]*scale[t,j], column 2j+1 =
 //   p[t]*midpoint[t,j] (codes are used centred on the group midpoint); one extra MMA with A = ones sums both columns.
@@ -128,7 +129,6 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
     __syncthreads();
     if (tail_lo < t1) qk_tail_mma(a, kf, b, hk, sm, t0, tail_lo, t1);
 
-    const uint32_t ones = 0x3c003c00u;
     for (int j = 0; j < my_tiles; ++j) {
         const int tile0 = t0 + (j * kMmaWarps + warp) * G::WT;
         const bool have_next = j + 1 < my_tiles;
@@ -140,8 +140,7 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
         __syncwarp();
         // ---- B fragments q*scale and the zero term sum_d q[d]*zero[d,g] ----------------------------------
         // q*scale needs 22 bits; it is carried as an fp16 pair hi + lo (lo = fma(q, s, -hi) is exact), so the key
-        // side adds no rounding beyond the fp32 accumulation.  The zero term gets the same treatment and is summed
-        // over channels by MMAs whose A operand is all ones (one accumulator per half of the pair: short chains).
+        // side adds no rounding beyond the fp32 accumulation.
         // 3-bit keys: b0 = hi and b1 = lo of the eight groups of the tile, every code tile is multiplied by both.
         // Other widths: b0 / b1 serve the first / second half of the tile; column n carries group (n / 2) of that
         // half, hi in even and lo in odd columns, so one MMA per code tile yields both parts.
@@ -153,17 +152,20 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
         const bool odd = g & 1;
 #pragma unroll
         for (int ksx = 0; ksx < 8; ++ksx) {
-            const __half2 q01 = as_h2(lds32(q_s + 32 * ksx)), q89 = as_h2(lds32(q_s + 32 * ksx + 16));
+            const uint32_t q01u = lds32(q_s + 32 * ksx), q89u = lds32(q_s + 32 * ksx + 16);
+            const __half2 q01 = as_h2(q01u), q89 = as_h2(q89u);
             // the tile rows are 8 groups x fp16 = one 8x8 matrix per 8 channels: a transposing ldmatrix hands
             // lane (g, tig) exactly {row 2tig, row 2tig+1} x column g, i.e. its B-fragment pairs of group g, in one go
             // (with fewer than 8 groups per tile the columns past the last group are stale and feed unused columns)
             uint32_t r0, r1, r2, r3;
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                          : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(ldm_s + ksx * 256));
-            const __half2 z01 = as_h2(r2), z89 = as_h2(r3);
-            const __half2 y01 = __hmul2(q01, z01), y89 = __hmul2(q89, z89);
-            mma16816(accz, ones, ones, ones, ones, as_u32(y01), as_u32(y89));
-            mma16816(accy, ones, ones, ones, ones, as_u32(__hfma2(q01, z01, __hneg2(y01))), as_u32(__hfma2(q89, z89, __hneg2(y89))));
+            // The zero terms: the same two registers are also the A fragment of the transposed zero tile (row = group g,
+            // k = channels 2tig, 2tig+1 / +8), so ONE MMA with B = q (in every column) leaves sum_d q[d] * zero[d, g] in
+            // row g; fp16 x fp16 products are exact in the tensor core, no hi / lo split is needed.  Two accumulators
+            // alternate to keep the chains short.  A stale group only spoils its own row.
+            if (ksx & 1) mma16816(accy, r2, 0u, r3, 0u, q01u, q89u);
+            else mma16816(accz, r2, 0u, r3, 0u, q01u, q89u);
             if constexpr (KB == 3) {
                 const __half2 s01 = as_h2(r0), s89 = as_h2(r1);
                 const __half2 p01 = __hmul2(q01, s01), p89 = __hmul2(q89, s89);
@@ -280,7 +282,7 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
             const int tok0 = tile0 + g * G::TPO;               // first token of this octet's chunk
             if (tok0 < hi && tig == (g >> 1)) {                // chunks are whole or absent (hi is a group multiple)
                 const bool sel = g & 1;
-                const float corr = sel ? accz[1] : accz[0];
+                const float corr = accz[0];                    // row g of the zero-term product = group g = this octet's word
                 float *dst = sm.scores + (tok0 - t0);
 #pragma unroll
                 for (int m = 0; m < G::NMMA; ++m) {
@@ -298,15 +300,13 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
             }
         } else if constexpr (KB == 4) {
             // octet g of half h is in group h*gph + cp of the tile, cp = 16 g / Gk; its hi and lo sums are the column
-            // pair cp, held by the lane with tig == cp; the group's zero term sits in another lane of the quad
+            // pair cp, held by the lane with tig == cp; the group's zero term sits in the lanes of octet grp
             constexpr int NF = F::N;
             const int cp = (16 * g) / Gk;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int grp = h * gph + cp;
-                const int zsrc = (lane & ~3) | ((grp >> 1) & 3);
-                const float z0 = __shfl_sync(0xffffffffu, accz[0], zsrc), z1 = __shfl_sync(0xffffffffu, accz[1], zsrc);
-                const float corr = (grp & 1) ? z1 : z0;
+                const float corr = __shfl_sync(0xffffffffu, accz[0], 4 * grp);    // row grp of the zero-term product
                 const int tok0 = tile0 + 128 * h + 16 * g;
                 if (tok0 < hi && tig == cp) {                  // 16-token chunks are whole or absent (hi is a group multiple)
                     float *dst = sm.scores + (tok0 - t0);
@@ -326,8 +326,8 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
             }
         } else {
             // octet g of block bb owns tokens bb*8FH + g*FH ..; in its half of the tile they are in group cp, whose hi and
-            // lo sums are the column pair cp, held by the lane with tig == cp; the group's zero term sits in another
-            // lane of the quad
+            // lo sums are the column pair cp, held by the lane with tig == cp; the group's zero term sits in the lanes
+            // of octet grp
             const int lgk = 31 - __clz(Gk);                    // group sizes are powers of two here
 #pragma unroll
             for (int bb = 0; bb < NBK; ++bb) {
@@ -335,9 +335,7 @@ __device__ __forceinline__ void qk_packed_mma(const kvq_attn_args &a, const int3
                 const int h = bb / kHalfBlocks;
                 const int cp = (((bb % kHalfBlocks) * 8 * FH) + g * FH) >> lgk;
                 const int grp = h * gph + cp;
-                const int zsrc = (lane & ~3) | ((grp >> 1) & 3);
-                const float z0 = __shfl_sync(0xffffffffu, accz[0], zsrc), z1 = __shfl_sync(0xffffffffu, accz[1], zsrc);
-                const float corr = (grp & 1) ? z1 : z0;
+                const float corr = __shfl_sync(0xffffffffu, accz[0], 4 * grp);    // row grp of the zero-term product
                 const int tok0 = tile0 + bb * 8 * FH + g * FH;
                 if (tok0 < hi && tig == cp) {                  // FH-token chunks are whole or absent (hi is a group multiple)
                     float *dst = sm.scores + (tok0 - t0);
