@@ -457,6 +457,8 @@ class CapturedDecodeStep:
             raise RuntimeError("a captured decode step needs caches made with device_state=True")
         if any(not c.steady() for c in caches):
             raise RuntimeError("a captured decode step needs caches in steady state (at most one group due per step)")
+        if peers is not None and len(caches) % peers.depth:
+            raise RuntimeError("the layers of a step must use the exchange buffers a whole number of rounds")
         self.caches, self.left, self.peers = list(caches), int(max_replays), peers
         self.gathered = [None] * len(caches)
         side = torch.cuda.Stream()
@@ -481,8 +483,6 @@ class CapturedDecodeStep:
         for c, m in zip(caches, mirrors):
             c.kv_seq_len, c.tkq, c.tvq, c.k_start, c.v_start, c.k_len, c.v_len = m
         if peers is not None:
-            if (peers.layer - layer0) % peers.depth:
-                raise RuntimeError("the layers of a step must use the exchange buffers a whole number of rounds")
             peers.layer = layer0
 
     def replay(self, steps=1):
